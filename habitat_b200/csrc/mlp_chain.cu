@@ -1,0 +1,697 @@
+// Fused inference of Habitat's per-operation MLP runtime predictors on sm_100a.
+//
+// Stands in for RuntimePredictor.predict (analyzer/habitat/analysis/mlp/mlp.py:252-267
+// of the reference) over a whole batch of queries: feature normalisation
+// (mlp.py:258-261), fc1 + ReLU, `layers` x [Linear(1024,1024) + ReLU] and fc2
+// (mlp.py:17-109) run as ONE persistent kernel; activations never leave the SM.
+//
+// Formulation.  Each CTA owns a tile of TILE_Q queries and computes every layer
+// transposed, H^T = W . X^T, so that
+//   A (M = 128 output features x K) = a weight tile, streamed from global/L2
+//                                     into a shared-memory ring by bulk async
+//                                     copies (TMA engine, mbarrier completion);
+//   B (N = TILE_Q queries x K)      = the activations, resident in shared memory
+//                                     in the K-major 128-byte-swizzled layout;
+//   D (128 lanes x TILE_Q columns)  = fp32 accumulators in tensor memory, one
+//                                     column block per 128-feature tile, so the
+//                                     whole layer output (1024 x TILE_Q) lives in
+//                                     TMEM until it is drained.
+// tcgen05.mma (kind::f16, bf16 inputs, fp32 accumulate) is issued by one thread;
+// the epilogue warps read TMEM with tcgen05.ld, add the bias, apply ReLU, round
+// to bf16 and overwrite the activation buffer in place - legal because the
+// complete layer output is parked in TMEM before the first write.  fc2 is a dot
+// product over features (= TMEM lanes), reduced through shared memory.
+//
+// fc1 has K = F + 4 <= 12.  Its inputs are the normalised features, which need
+// more than bf16's 8 bits, so both x and w are split into bf16 hi + lo parts and
+// the three products hi.hi + lo.hi + hi.lo are laid side by side along K
+// (3 (F+4) <= 36 of the 64 columns of one K block).
+//
+// Precision modes: HB_PRECISION_BF16 rounds hidden activations and weights to
+// bf16 (TILE_Q = 64); HB_PRECISION_BF16X3 keeps hi + lo parts of both and issues
+// the same three-product expansion for every hidden layer (TILE_Q = 32).
+//
+// Warp roles (192 threads): warp 0 = TMEM allocation + weight producer,
+// warp 1 = barrier set-up + MMA issuer, warps 2-5 = epilogue (one TMEM lane
+// quadrant each).  Every mbarrier wait is bounded: when a wait runs out the
+// kernel records a status word, all roles leave their loops, outstanding bulk
+// copies are waited for (bounded) and TMEM is released.
+#include <cuda_bf16.h>
+
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "hb_common.h"
+
+namespace {
+
+constexpr int kWidth = 1024;            // layer_size of every Habitat predictor
+constexpr int kMTile = 128;             // output features per MMA (TMEM lanes)
+constexpr int kKBlk = 64;               // bf16 per 128-byte swizzle row
+constexpr int kNumMT = kWidth / kMTile; // 8
+constexpr int kNumKB = kWidth / kKBlk;  // 16
+constexpr int kTileBytes = kMTile * 128;// one weight tile image: 16 KB
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kMaxInFeat = 12;          // F + 4 (conv2d: 8 + 4)
+
+template <int TILE_Q, bool SPLIT>
+struct Cfg {
+  static constexpr int kActKbBytes = TILE_Q * 128;             // one K block of activations
+  static constexpr int kActBytes = kNumKB * kActKbBytes;       // hi (or only) copy
+  static constexpr int kActCopies = SPLIT ? 2 : 1;
+  static constexpr int kStageBytes = kTileBytes * (SPLIT ? 2 : 1);
+  static constexpr int kStages = SPLIT ? 3 : 6;
+  static constexpr int kBarBytes = 1024;
+  static constexpr int kSmemBytes =
+      kActBytes * kActCopies + kStages * kStageBytes + kBarBytes + 1024 /* alignment slack */;
+  static constexpr int kTmemCols = kNumMT * TILE_Q;            // 512 or 256
+  static_assert(kTmemCols == 512 || kTmemCols == 256, "TMEM allocation must be a power of two");
+  static_assert(kSmemBytes <= 232448, "over the 227 KB shared-memory limit");
+};
+
+struct MlpParams {
+  const uint8_t* wpack;      // weight tile images, producer order
+  const float* bias;         // [layers + 1][1024]: fc1, hidden...
+  const float* fc2_w;        // [1024]
+  float fc2_b;
+  const double* mu;          // [F + 4]
+  const double* sigma;       // [F + 4]
+  const double* dev_feat;    // [n_dev][4]
+  int32_t n_dev;
+  int32_t n_op_feat;         // F
+  int32_t layers;            // hidden layers
+  const float* feats;        // [Q][F]
+  const uint8_t* dev_row;    // [Q]
+  int64_t Q;
+  float* out;                // [Q]
+  int32_t num_tiles;
+  int32_t* status;           // device word: 0 ok, else (role << 8 | site)
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane
+// (quadrant base + t), registers = columns.
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  tc_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows are 128 B
+// apart, groups of 8 rows 1024 B apart (the stride byte offset); the leading
+// byte offset is unused for swizzled K-major operands; descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);  // start address
+  d |= static_cast<uint64_t>(1) << 16;                 // leading byte offset (16 B units)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;         // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                 // version
+  d |= static_cast<uint64_t>(2) << 61;                 // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: D = fp32, A = B = bf16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(kMTile >> 4) << 24);
+}
+
+// Byte offset of element (row, col) inside a K-major 128-byte-swizzled block of
+// 128-byte rows: 16-byte chunks are permuted by the row index modulo 8.
+__host__ __device__ __forceinline__ uint32_t swz_off(uint32_t row, uint32_t col) {
+  return row * 128u + ((((col >> 3) ^ row) & 7u) << 4) + ((col & 7u) << 1);
+}
+
+constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
+
+// Bounded wait.  Returns false when the wait ran out or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void epi_bar_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------
+template <int TILE_Q, bool SPLIT>
+__global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_constant__ MlpParams p) {
+  using C = Cfg<TILE_Q, SPLIT>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+
+  const uint32_t act_hi = base;
+  const uint32_t act_lo = base + C::kActBytes;  // SPLIT only
+  const uint32_t stage0 = base + C::kActBytes * C::kActCopies;
+  const uint32_t bars = stage0 + C::kStages * C::kStageBytes;
+  uint8_t* bars_ptr = base_ptr + (bars - base);
+  // barrier block: full[stages], empty[stages], acc_full, act_ready, then words
+  const uint32_t bar_full = bars;
+  const uint32_t bar_empty = bars + 8 * C::kStages;
+  const uint32_t bar_acc = bars + 16 * C::kStages;
+  const uint32_t bar_act = bar_acc + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 16 * C::kStages + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 16 * C::kStages + 20);
+  volatile int* epi_ok = reinterpret_cast<volatile int*>(bars_ptr + 16 * C::kStages + 24);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 32) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    mbar_init(bar_act, kEpiThreads);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_layers = p.layers + 1;  // fc1 + hidden
+  int my_tiles = 0;
+  if (static_cast<int>(blockIdx.x) < p.num_tiles)
+    my_tiles = (p.num_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1;
+
+  uint32_t issued = 0;  // producer: stage loads issued (for the drain at exit)
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        const uint8_t* src = p.wpack;
+        for (int L = 0; L < n_layers && ok; ++L) {
+          const int n_loads = kNumMT * (L == 0 ? 1 : kNumKB);
+          for (int i = 0; i < n_loads; ++i, ++it) {
+            const uint32_t s = it % C::kStages;
+            const uint32_t ph = (it / C::kStages) & 1u;
+            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 0x101)) { ok = false; break; }
+            mbar_expect_tx(bar_full + 8 * s, C::kStageBytes);
+            bulk_g2s(stage0 + s * C::kStageBytes, src, C::kStageBytes, bar_full + 8 * s);
+            src += C::kStageBytes;
+          }
+        }
+      }
+      issued = it;
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ----------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(TILE_Q);
+      uint32_t it = 0, lay = 0;
+      bool ok = true;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        for (int L = 0; L < n_layers && ok; ++L, ++lay) {
+          if (!mbar_wait(bar_act, lay & 1u, abort_flag, p.status, 0x201)) { ok = false; break; }
+          tc_fence_after();
+          const int nkb = L == 0 ? 1 : kNumKB;
+          for (int mt = 0; mt < kNumMT && ok; ++mt) {
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(mt * TILE_Q);
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+              const uint32_t s = it % C::kStages;
+              const uint32_t ph = (it / C::kStages) & 1u;
+              if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x202)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t a_base = stage0 + s * C::kStageBytes;
+              const uint32_t b_base = act_hi + kb * C::kActKbBytes;
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) {
+                const uint64_t a_hi = smem_desc_k128(a_base + ks * 32);
+                const uint64_t b_hi = smem_desc_k128(b_base + ks * 32);
+                tc_mma_bf16(d_tmem, a_hi, b_hi, idesc, (kb | ks) != 0 ? 1u : 0u);
+                if (SPLIT && L > 0) {
+                  const uint64_t a_lo = smem_desc_k128(a_base + kTileBytes + ks * 32);
+                  const uint64_t b_lo = smem_desc_k128(act_lo + kb * C::kActKbBytes + ks * 32);
+                  tc_mma_bf16(d_tmem, a_hi, b_lo, idesc, 1u);
+                  tc_mma_bf16(d_tmem, a_lo, b_hi, idesc, 1u);
+                }
+              }
+              tc_commit(bar_empty + 8 * s);  // frees the ring slot once these MMAs retire
+            }
+          }
+          if (ok) tc_commit(bar_acc);  // the whole layer sits in TMEM
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int e = threadIdx.x - 64;            // 0..127
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int r = quad * 32 + lane;            // feature row inside a 128-feature tile
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const int C_in = p.n_op_feat + 4;
+    uint32_t lay = 0;
+    bool ok = true;
+    float* red = reinterpret_cast<float*>(base_ptr);  // [128][TILE_Q + 1], aliases activations
+
+    for (int t = 0; t < my_tiles && ok; ++t) {
+      const int tile = static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x);
+      const int64_t q0 = static_cast<int64_t>(tile) * TILE_Q;
+
+      // ---- normalised, split input features -> K block 0 (mlp.py:258-261) ----
+      if (e < TILE_Q) {
+        const int64_t q = q0 + e;
+        __nv_bfloat16 row[kKBlk];
+#pragma unroll
+        for (int c = 0; c < kKBlk; ++c) row[c] = __float2bfloat16_rn(0.0f);
+        if (q < p.Q) {
+          int dr = p.dev_row[q];
+          dr = dr < p.n_dev ? dr : p.n_dev - 1;
+          for (int c = 0; c < C_in; ++c) {
+            const double x = c < p.n_op_feat
+                                 ? static_cast<double>(p.feats[q * p.n_op_feat + c])
+                                 : p.dev_feat[dr * 4 + (c - p.n_op_feat)];
+            const float xn = static_cast<float>((x - p.mu[c]) / p.sigma[c]);
+            const __nv_bfloat16 hi = __float2bfloat16_rn(xn);
+            const __nv_bfloat16 lo = __float2bfloat16_rn(xn - __bfloat162float(hi));
+            row[c] = hi;
+            row[C_in + c] = lo;
+            row[2 * C_in + c] = hi;
+          }
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(row);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint4* dst = reinterpret_cast<uint4*>(base_ptr + e * 128 + (((ch ^ e) & 7) << 4));
+          *dst = src[ch];
+        }
+      }
+      fence_proxy_async();
+      mbar_arrive(bar_act);
+
+      for (int L = 0; L < n_layers && ok; ++L, ++lay) {
+        // One thread waits and hands the verdict to the other 127 through the
+        // named barrier, so the whole group takes the same branch.
+        if (e == 0) *epi_ok = mbar_wait(bar_acc, lay & 1u, abort_flag, p.status, 0x301) ? 1 : 0;
+        epi_bar_sync();
+        if (*epi_ok == 0) { ok = false; break; }
+        tc_fence_after();
+        const float* bias = p.bias + L * kWidth;
+        const bool last = (L == n_layers - 1);
+        if (!last) {
+          // bias + ReLU + bf16, written back as the next layer's B operand
+#pragma unroll 1
+          for (int mt = 0; mt < kNumMT; ++mt) {
+            const float b = __ldg(bias + mt * kMTile + r);
+            const int f = mt * kMTile + r;                 // feature = K index of the next layer
+            const uint32_t kb_off = static_cast<uint32_t>(f >> 6) * C::kActKbBytes;
+            const uint32_t col = static_cast<uint32_t>(f & 63);
+#pragma unroll
+            for (int h = 0; h < TILE_Q / 32; ++h) {
+              float v[32];
+              tc_ld32(t_lane + static_cast<uint32_t>(mt * TILE_Q + h * 32), v);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const uint32_t n = static_cast<uint32_t>(h * 32 + i);
+                const float x = fmaxf(v[i] + b, 0.0f);
+                const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+                const uint32_t off = kb_off + swz_off(n, col);
+                *reinterpret_cast<__nv_bfloat16*>(base_ptr + off) = hi;
+                if (SPLIT) {
+                  const __nv_bfloat16 lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+                  *reinterpret_cast<__nv_bfloat16*>(base_ptr + C::kActBytes + off) = lo;
+                }
+              }
+            }
+          }
+          tc_fence_before();
+          fence_proxy_async();
+          mbar_arrive(bar_act);
+        } else {
+          // fc2 (mlp.py:46-48): dot over features = over TMEM lanes and tiles
+          float acc[TILE_Q];
+#pragma unroll
+          for (int i = 0; i < TILE_Q; ++i) acc[i] = 0.0f;
+#pragma unroll 1
+          for (int mt = 0; mt < kNumMT; ++mt) {
+            const float b = __ldg(bias + mt * kMTile + r);
+            const float w = __ldg(p.fc2_w + mt * kMTile + r);
+#pragma unroll
+            for (int h = 0; h < TILE_Q / 32; ++h) {
+              float v[32];
+              tc_ld32(t_lane + static_cast<uint32_t>(mt * TILE_Q + h * 32), v);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc[h * 32 + i] = fmaf(w, fmaxf(v[i] + b, 0.0f), acc[h * 32 + i]);
+            }
+          }
+          tc_fence_before();
+          // every MMA of this tile has retired, so the activation buffer is free
+#pragma unroll
+          for (int i = 0; i < TILE_Q; ++i) red[r * (TILE_Q + 1) + i] = acc[i];
+          epi_bar_sync();
+          {
+            const int n = e % TILE_Q;
+            const int part = e / TILE_Q;               // 128 / TILE_Q partial sums per query
+            constexpr int kParts = kEpiThreads / TILE_Q;
+            constexpr int kRows = kMTile / kParts;
+            float s = 0.0f;
+            for (int j = 0; j < kRows; ++j) s += red[(part * kRows + j) * (TILE_Q + 1) + n];
+            epi_bar_sync();                            // all reads of `red` done
+            red[part * TILE_Q + n] = s;
+            epi_bar_sync();
+            if (e < TILE_Q) {
+              float tot = p.fc2_b;
+              for (int j = 0; j < kParts; ++j) tot += red[j * TILE_Q + e];
+              const int64_t q = q0 + e;
+              if (q < p.Q) p.out[q] = tot;
+            }
+            epi_bar_sync();                            // `red` may be overwritten again
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    if (lane == 0 && *abort_flag) {
+      // a role gave up: wait (bounded) for bulk copies that are still landing
+      const uint32_t first = issued > static_cast<uint32_t>(C::kStages) ? issued - C::kStages : 0;
+      for (uint32_t j = first; j < issued; ++j) {
+        const uint32_t s = j % C::kStages, ph = (j / C::kStages) & 1u;
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar_full + 8 * s, ph)) {
+          if (clock64() - t0 > kWaitCycles) break;
+        }
+      }
+    }
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: weight packing and launch
+// ---------------------------------------------------------------------------
+uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  if ((u & 0x7F800000u) == 0x7F800000u && (u & 0x007FFFFFu)) return static_cast<uint16_t>((u >> 16) | 0x40);
+  const uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7FFFu + lsb;
+  return static_cast<uint16_t>(u >> 16);
+}
+float bf16_to_f32(uint16_t h) {
+  const uint32_t u = static_cast<uint32_t>(h) << 16;
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+
+void put(uint8_t* tile, int row, int col, uint16_t v) {
+  std::memcpy(tile + swz_off(static_cast<uint32_t>(row), static_cast<uint32_t>(col)), &v, 2);
+}
+
+}  // namespace
+
+struct hb_mlp {
+  int32_t n_op_feat = 0, layers = 0, precision = 0, n_dev = 0, sm_count = 0, device = 0;
+  float fc2_b = 0.f;
+  uint8_t* wpack = nullptr;
+  float* bias = nullptr;
+  float* fc2_w = nullptr;
+  double* mu = nullptr;
+  double* sigma = nullptr;
+  double* dev_feat = nullptr;
+  int32_t* status = nullptr;
+};
+
+extern "C" void hb_mlp_destroy(hb_mlp* h) {
+  if (!h) return;
+  cudaFree(h->wpack); cudaFree(h->bias); cudaFree(h->fc2_w); cudaFree(h->mu);
+  cudaFree(h->sigma); cudaFree(h->dev_feat); cudaFree(h->status);
+  delete h;
+}
+
+extern "C" hb_status hb_mlp_create(hb_mlp** handle, int32_t n_op_features, int32_t layers,
+                                   int32_t width, const float* fc1_w, const float* fc1_b,
+                                   const float* hidden_w, const float* hidden_b,
+                                   const float* fc2_w, const float* fc2_b, const double* mu,
+                                   const double* sigma, const double* device_features,
+                                   int32_t n_device_rows, int32_t precision) {
+  if (!handle || !fc1_w || !fc1_b || (layers > 0 && (!hidden_w || !hidden_b)) || !fc2_w || !fc2_b ||
+      !mu || !sigma || !device_features) {
+    hb::set_error("hb_mlp_create: NULL argument");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  if (width != kWidth || layers < 1 || layers > 64 || n_op_features < 1 ||
+      n_op_features + 4 > kMaxInFeat || n_device_rows < 1 || n_device_rows > 256 ||
+      (precision != HB_PRECISION_BF16 && precision != HB_PRECISION_BF16X3)) {
+    hb::set_error("hb_mlp_create: unsupported shape (width must be 1024, 1 <= F <= 8, layers >= 1)");
+    return HB_ERR_UNSUPPORTED;
+  }
+  const bool split = precision == HB_PRECISION_BF16X3;
+  const int C_in = n_op_features + 4;
+  const size_t img = split ? 2 * kTileBytes : kTileBytes;
+  const size_t n_img = kNumMT + static_cast<size_t>(layers) * kNumMT * kNumKB;
+  std::vector<uint8_t> pack(n_img * img, 0);
+  uint8_t* dst = pack.data();
+  // fc1: [w_hi | w_hi | w_lo] along K, matching the activations' [x_hi | x_lo | x_hi]
+  for (int mt = 0; mt < kNumMT; ++mt, dst += img) {
+    for (int rr = 0; rr < kMTile; ++rr) {
+      const float* wrow = fc1_w + static_cast<size_t>(mt * kMTile + rr) * C_in;
+      for (int c = 0; c < C_in; ++c) {
+        const uint16_t hi = f32_to_bf16(wrow[c]);
+        const uint16_t lo = f32_to_bf16(wrow[c] - bf16_to_f32(hi));
+        put(dst, rr, c, hi);
+        put(dst, rr, C_in + c, hi);
+        put(dst, rr, 2 * C_in + c, lo);
+      }
+    }
+  }
+  for (int L = 0; L < layers; ++L) {
+    const float* W = hidden_w + static_cast<size_t>(L) * kWidth * kWidth;
+    for (int mt = 0; mt < kNumMT; ++mt) {
+      for (int kb = 0; kb < kNumKB; ++kb, dst += img) {
+        for (int rr = 0; rr < kMTile; ++rr) {
+          const float* wrow = W + static_cast<size_t>(mt * kMTile + rr) * kWidth + kb * kKBlk;
+          for (int c = 0; c < kKBlk; ++c) {
+            const uint16_t hi = f32_to_bf16(wrow[c]);
+            put(dst, rr, c, hi);
+            if (split) put(dst + kTileBytes, rr, c, f32_to_bf16(wrow[c] - bf16_to_f32(hi)));
+          }
+        }
+      }
+    }
+  }
+
+  hb_mlp* h = new hb_mlp();
+  h->n_op_feat = n_op_features;
+  h->layers = layers;
+  h->precision = precision;
+  h->n_dev = n_device_rows;
+  h->fc2_b = fc2_b[0];
+  auto fail = [&](cudaError_t e, const char* what) {
+    hb_status st = hb::cuda_fail(e, what);
+    hb_mlp_destroy(h);
+    return st;
+  };
+  cudaError_t e;
+  if ((e = cudaGetDevice(&h->device)) != cudaSuccess) return fail(e, "cudaGetDevice");
+  if ((e = cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, h->device)) != cudaSuccess)
+    return fail(e, "cudaDeviceGetAttribute");
+  std::vector<float> bias(static_cast<size_t>(layers + 1) * kWidth);
+  std::memcpy(bias.data(), fc1_b, sizeof(float) * kWidth);
+  std::memcpy(bias.data() + kWidth, hidden_b, sizeof(float) * kWidth * layers);
+#define HB_UP(field, src, bytes)                                                        \
+  if ((e = cudaMalloc(reinterpret_cast<void**>(&h->field), (bytes))) != cudaSuccess)    \
+    return fail(e, "cudaMalloc " #field);                                               \
+  if ((e = cudaMemcpy(h->field, (src), (bytes), cudaMemcpyHostToDevice)) != cudaSuccess) \
+    return fail(e, "cudaMemcpy " #field);
+  HB_UP(wpack, pack.data(), pack.size());
+  HB_UP(bias, bias.data(), bias.size() * sizeof(float));
+  HB_UP(fc2_w, fc2_w, sizeof(float) * kWidth);
+  HB_UP(mu, mu, sizeof(double) * C_in);
+  HB_UP(sigma, sigma, sizeof(double) * C_in);
+  HB_UP(dev_feat, device_features, sizeof(double) * 4 * n_device_rows);
+#undef HB_UP
+  if ((e = cudaMalloc(reinterpret_cast<void**>(&h->status), sizeof(int32_t))) != cudaSuccess)
+    return fail(e, "cudaMalloc status");
+  if ((e = cudaMemset(h->status, 0, sizeof(int32_t))) != cudaSuccess) return fail(e, "cudaMemset");
+  e = cudaFuncSetAttribute(mlp_chain_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           Cfg<64, false>::kSmemBytes);
+  if (e != cudaSuccess) return fail(e, "cudaFuncSetAttribute");
+  e = cudaFuncSetAttribute(mlp_chain_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           Cfg<32, true>::kSmemBytes);
+  if (e != cudaSuccess) return fail(e, "cudaFuncSetAttribute");
+  *handle = h;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_mlp_predict(hb_mlp* h, const float* op_features, const uint8_t* device_row,
+                                    int64_t Q, float* out, void* stream) {
+  if (!h || Q < 0 || (Q > 0 && (!op_features || !device_row || !out))) {
+    hb::set_error("hb_mlp_predict: bad arguments");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  if (Q == 0) return HB_OK;
+  const bool split = h->precision == HB_PRECISION_BF16X3;
+  const int tile_q = split ? 32 : 64;
+  const int64_t tiles = (Q + tile_q - 1) / tile_q;
+  if (tiles > 0x7FFFFFFF) {
+    hb::set_error("hb_mlp_predict: Q too large for one launch");
+    return HB_ERR_TOO_LARGE;
+  }
+  MlpParams p{};
+  p.wpack = h->wpack; p.bias = h->bias; p.fc2_w = h->fc2_w; p.fc2_b = h->fc2_b;
+  p.mu = h->mu; p.sigma = h->sigma; p.dev_feat = h->dev_feat; p.n_dev = h->n_dev;
+  p.n_op_feat = h->n_op_feat; p.layers = h->layers; p.feats = op_features;
+  p.dev_row = device_row; p.Q = Q; p.out = out; p.num_tiles = static_cast<int32_t>(tiles);
+  p.status = h->status;
+  const int grid = static_cast<int>(tiles < h->sm_count ? tiles : h->sm_count);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (split) mlp_chain_kernel<32, true><<<grid, kThreads, Cfg<32, true>::kSmemBytes, s>>>(p);
+  else mlp_chain_kernel<64, false><<<grid, kThreads, Cfg<64, false>::kSmemBytes, s>>>(p);
+  HB_CUDA_TRY(cudaGetLastError());
+  return HB_OK;
+}
+
+extern "C" hb_status hb_mlp_status(hb_mlp* h, int32_t* device_status) {
+  if (!h || !device_status) {
+    hb::set_error("hb_mlp_status: NULL argument");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  HB_CUDA_TRY(cudaMemcpy(device_status, h->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  if (*device_status != 0) {
+    hb::set_error("mlp kernel: a bounded device-side wait ran out (site 0x%x)", *device_status);
+    return HB_ERR_DEVICE_TIMEOUT;
+  }
+  return HB_OK;
+}
+
+extern "C" hb_status hb_mlp_predict_host(hb_mlp* h, const float* op_features,
+                                         const uint8_t* device_row, int64_t Q, float* out) {
+  if (!h || Q < 0 || (Q > 0 && (!op_features || !device_row || !out))) {
+    hb::set_error("hb_mlp_predict_host: bad arguments");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  if (Q == 0) return HB_OK;
+  float* d_f = nullptr; uint8_t* d_r = nullptr; float* d_o = nullptr;
+  const size_t fb = sizeof(float) * static_cast<size_t>(Q) * h->n_op_feat;
+  hb_status st = HB_OK;
+  cudaError_t e;
+  if ((e = cudaMalloc(reinterpret_cast<void**>(&d_f), fb)) != cudaSuccess ||
+      (e = cudaMalloc(reinterpret_cast<void**>(&d_r), static_cast<size_t>(Q))) != cudaSuccess ||
+      (e = cudaMalloc(reinterpret_cast<void**>(&d_o), sizeof(float) * static_cast<size_t>(Q))) != cudaSuccess ||
+      (e = cudaMemcpyAsync(d_f, op_features, fb, cudaMemcpyHostToDevice, nullptr)) != cudaSuccess ||
+      (e = cudaMemcpyAsync(d_r, device_row, static_cast<size_t>(Q), cudaMemcpyHostToDevice, nullptr)) != cudaSuccess) {
+    st = hb::cuda_fail(e, "hb_mlp_predict_host: staging");
+  }
+  if (st == HB_OK) st = hb_mlp_predict(h, d_f, d_r, Q, d_o, nullptr);
+  if (st == HB_OK &&
+      (e = cudaMemcpy(out, d_o, sizeof(float) * static_cast<size_t>(Q), cudaMemcpyDeviceToHost)) != cudaSuccess)
+    st = hb::cuda_fail(e, "hb_mlp_predict_host: copy back");
+  if (st == HB_OK) {
+    int32_t code = 0;
+    st = hb_mlp_status(h, &code);
+  }
+  cudaFree(d_f); cudaFree(d_r); cudaFree(d_o);
+  return st;
+}

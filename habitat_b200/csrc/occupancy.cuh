@@ -1,0 +1,187 @@
+// Thread-block occupancy as Habitat computes it, for device (and host) code.
+//
+// Behavioural equivalent of KernelMetadata::threadBlockOccupancy
+// (cpp/src/cuda/kernel.cpp:33-56 of the reference), which calls NVIDIA's
+// standalone occupancy calculator with partitioned global caching off, the
+// default shared-memory limit and carve-out, and unlimited per-function block
+// size and dynamic shared memory.  Compute capability 3/5/6/7 follows the
+// rules of the header the reference vendors; 8/9/10/12, which that header
+// rejects, follow the CUDA 12 toolkit header with its per-block reserved
+// shared memory.  All arithmetic is integer and must match bit for bit.
+//
+// Everything that depends only on the device row is folded once, on the host,
+// into an hb_dev_pre; the per-kernel part is hb_occupancy().
+#pragma once
+
+#include <cstdint>
+
+#include "habitat_b200.h"
+
+#if defined(__CUDACC__)
+#define HB_HD __host__ __device__ __forceinline__
+#else
+#define HB_HD inline
+#endif
+
+#define HB_INT_MAX 0x7FFFFFFF
+
+// Per-device constants of the occupancy rules (one row of constant memory).
+struct hb_dev_pre {
+  int32_t valid;            // row passes the calculator's input checks
+  int32_t warp_size;
+  int32_t warp_shift;       // log2(warp_size) if a power of two, else -1
+  int32_t parts;            // register-file sub-partitions per SM
+  int32_t gp100;            // cc 6.0: re-check the register limit with 4 parts
+  int32_t regs_per_block;
+  int32_t regs_per_part;    // regs_per_multiprocessor / parts
+  int32_t regs_per_part4;   // regs_per_multiprocessor / 4
+  int32_t max_warps;        // max_threads_per_multiprocessor / warp_size
+  int32_t max_threads_per_block;
+  int32_t blocks_limit;
+  int32_t smem_gran;        // allocation granularity, bytes
+  int32_t smem_reserved;    // driver-reserved bytes per block (cc >= 8)
+  int32_t smem_cap;         // per-block cap incl. the reserved bytes
+  int32_t smem_pref;        // configured per-SM carve-out (snapped), < 0: error
+  int32_t ladder_kind;      // which carve-out ladder applies (see hb_carveout_snap)
+  int32_t smem_per_sm;
+  int32_t num_sms;
+};
+
+// Ladder kinds: 0 none (cc < 7: fixed per-SM size), 1 Volta, 2 Turing,
+// 3: {..64,100} KB, 4: {..64,100,132,164} KB, 5: {..64,100,...,228} KB.
+HB_HD int32_t hb_carveout_snap(int32_t kind, int32_t smem_per_sm, int32_t size) {
+  if (kind == 2) return size <= 32768 ? 32768 : smem_per_sm;
+  if (size == 0) return 0;
+  if (size <= 8192) return 8192;
+  if (size <= 16384) return 16384;
+  if (size <= 32768) return 32768;
+  if (size <= 65536) return 65536;
+  if (kind == 1) return smem_per_sm;
+  if (size <= 100 * 1024) return 100 * 1024;
+  if (kind == 3) return -1;
+  if (size <= 132 * 1024) return 132 * 1024;
+  if (size <= 164 * 1024) return 164 * 1024;
+  if (kind == 4) return -1;
+  if (size <= 196 * 1024) return 196 * 1024;
+  if (size <= 228 * 1024) return 228 * 1024;
+  return -1;
+}
+
+// Folds one device row.  Host only: runs when the table is uploaded.
+inline hb_dev_pre hb_fold_device(const hb_device_spec& s) {
+  hb_dev_pre p{};
+  const int major = s.compute_major, minor = s.compute_minor;
+  bool ok = s.max_threads_per_block > 0 && s.max_threads_per_multiprocessor > 0 &&
+            s.regs_per_block > 0 && s.regs_per_multiprocessor > 0 && s.warp_size > 0 &&
+            s.shared_mem_per_block > 0 && s.shared_mem_per_multiprocessor > 0 && s.num_sms > 0;
+  ok = ok && (major == 3 || (major >= 5 && major <= 10) || major == 12);
+  p.num_sms = s.num_sms;
+  p.smem_per_sm = s.shared_mem_per_multiprocessor;
+  if (!ok) return p;
+  p.warp_size = s.warp_size;
+  p.warp_shift = -1;
+  for (int b = 0; b < 16; ++b)
+    if (s.warp_size == (1 << b)) p.warp_shift = b;
+  p.gp100 = (major == 6 && minor == 0) ? 1 : 0;
+  p.parts = p.gp100 ? 2 : 4;
+  p.regs_per_block = s.regs_per_block;
+  p.regs_per_part = s.regs_per_multiprocessor / p.parts;
+  p.regs_per_part4 = s.regs_per_multiprocessor / 4;
+  p.max_warps = s.max_threads_per_multiprocessor / s.warp_size;
+  p.max_threads_per_block = s.max_threads_per_block;
+  switch (major) {
+    case 3: p.blocks_limit = 16; break;
+    case 5: case 6: p.blocks_limit = 32; break;
+    case 7: p.blocks_limit = minor == 5 ? 16 : 32; break;
+    case 8: p.blocks_limit = minor == 0 ? 32 : (minor == 9 ? 24 : 16); break;
+    case 9: p.blocks_limit = 32; break;
+    case 10: p.blocks_limit = minor == 1 ? 24 : 32; break;
+    default: p.blocks_limit = 24; break;  // 12
+  }
+  p.smem_gran = major >= 8 ? 128 : 256;
+  p.smem_reserved = major >= 8 ? s.reserved_shared_mem_per_block : 0;
+  p.smem_cap = s.shared_mem_per_block + p.smem_reserved;
+  if (major < 7) {
+    p.ladder_kind = 0;
+    p.smem_pref = s.shared_mem_per_multiprocessor;
+  } else {
+    int kind = -1;
+    if (major == 7) kind = minor == 5 ? 2 : 1;
+    else if (major == 8) kind = (minor == 0 || minor == 7) ? 4 : 3;
+    else if (major == 9) kind = 5;
+    else if (major == 10) kind = (minor == 0 || minor == 1 || minor == 3) ? 5 : -1;
+    else if (major == 12) kind = (minor == 0 || minor == 1) ? 3 : -1;
+    if (kind < 0) return p;  // the calculator reports an unknown device
+    p.ladder_kind = kind;
+    p.smem_pref = hb_carveout_snap(kind, s.shared_mem_per_multiprocessor,
+                                   s.shared_mem_per_multiprocessor);
+    if (p.smem_pref < 0) return p;
+  }
+  p.valid = 1;
+  return p;
+}
+
+// Exact quotient n / d for n >= 0, d >= 1.  Below 2^22 the quotient comes from
+// one reciprocal and a remainder fix-up instead of a full integer division.
+HB_HD int32_t hb_div_small(int32_t n, int32_t d) {
+#if defined(__CUDA_ARCH__)
+  if (n >= (1 << 22)) return n / d;
+  int32_t q = __float2int_rz(__int2float_rn(n) * __frcp_rn(__int2float_rn(d)));
+  int32_t r = n - q * d;
+  if (r < 0) --q;
+  else if (r >= d) ++q;
+  return q;
+#else
+  return n / d;
+#endif
+}
+
+// Returns active blocks per SM; lim[4] = {regs, warps, blocks, smem} (all 0 on
+// error).  `regs` may differ per device (kernel metadata look-up).
+HB_HD int32_t hb_occupancy(const hb_dev_pre& d, int32_t block_size, int32_t smem, int32_t regs,
+                           int32_t lim[4]) {
+  lim[0] = lim[1] = lim[2] = lim[3] = 0;
+  if (!d.valid || block_size <= 0 || regs < 0) return 0;
+
+  const int32_t wpb = d.warp_shift >= 0 ? (block_size + d.warp_size - 1) >> d.warp_shift
+                                        : (block_size + d.warp_size - 1) / d.warp_size;
+  // registers
+  int32_t lr = 0;
+  if (regs <= 256) {
+    const int32_t rpw = ((regs * d.warp_size + 255) >> 8) << 8;
+    const int32_t wpb_up = ((wpb + d.parts - 1) / d.parts) * d.parts;
+    const int64_t per_cta = (int64_t)rpw * wpb;
+    const int64_t assumed = (int64_t)rpw * wpb_up;
+    if (!(d.regs_per_block < assumed || d.regs_per_block < per_cta)) {
+      if (rpw > 0) {
+        lr = (hb_div_small(d.regs_per_part, rpw) * d.parts) / wpb;
+        if (d.gp100 && lr != 0) {
+          const int64_t assumed4 = (int64_t)rpw * (((wpb + 3) >> 2) << 2);
+          if (d.regs_per_block < assumed4 || (d.regs_per_part4 / rpw) * 4 / wpb == 0) lr = 0;
+        }
+      } else {
+        lr = HB_INT_MAX;
+      }
+    }
+  }
+  // warps
+  const int32_t lw = block_size > d.max_threads_per_block ? 0 : d.max_warps / wpb;
+  // shared memory
+  int32_t ls = 0;
+  if (smem >= 0) {
+    const int32_t alloc = ((smem + d.smem_reserved + d.smem_gran - 1) / d.smem_gran) * d.smem_gran;
+    if (alloc <= d.smem_cap) {
+      int32_t budget = d.smem_pref;
+      if (budget < alloc) {
+        budget = d.ladder_kind == 0 ? d.smem_per_sm
+                                    : hb_carveout_snap(d.ladder_kind, d.smem_per_sm, alloc);
+        if (budget < 0) return 0;
+      }
+      ls = alloc > 0 ? budget / alloc : HB_INT_MAX;
+    }
+  }
+  lim[0] = lr; lim[1] = lw; lim[2] = d.blocks_limit; lim[3] = ls;
+  int32_t occ = lr < ls ? lr : ls;
+  occ = occ < lw ? occ : lw;
+  return occ < d.blocks_limit ? occ : d.blocks_limit;
+}

@@ -1,0 +1,160 @@
+// Trace-level totals and the special-operation ratio: small reduction and
+// elementwise kernels that follow the two big ones on the same stream.
+//
+// hb_segment_sum stands in for Trace.run_time_ms / RunTimePrediction.run_time_ms
+// (analyzer/habitat/analysis/trace.py:26-36, run_time.py:49-58) over many
+// segments at once; hb_special_scale for the last line of
+// Predictor._{conv2d,linear,bmm,lstm}_scale and the clamp in _special_scale
+// (analysis/predictor.py:132-148, :182).
+//
+// Sums are accumulated in float64 with a fixed assignment of elements to lanes
+// and a fixed reduction tree, so the result does not depend on grid size or
+// scheduling (no floating-point atomics).
+#include "hb_common.h"
+
+namespace {
+
+constexpr int kSumThreads = 256;
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+// Block-wide sum of one value per thread; valid in thread 0.
+__device__ __forceinline__ double block_sum(double v) {
+  __shared__ double s[kSumThreads / 32];
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+  __syncthreads();
+  double t = 0.0;
+  if (threadIdx.x < 32) {
+    t = threadIdx.x < kSumThreads / 32 ? s[threadIdx.x] : 0.0;
+    t = warp_sum(t);
+  }
+  __syncthreads();
+  return t;
+}
+
+// One block per segment.
+__global__ void __launch_bounds__(kSumThreads)
+segment_sum_kernel(const float* __restrict__ values, const int64_t* __restrict__ offsets,
+                   int64_t n_segments, double* __restrict__ out) {
+  for (int64_t s = blockIdx.x; s < n_segments; s += gridDim.x) {
+    const int64_t lo = offsets[s], hi = offsets[s + 1];
+    double acc = 0.0;
+    for (int64_t i = lo + threadIdx.x; i < hi; i += kSumThreads) acc += static_cast<double>(values[i]);
+    const double t = block_sum(acc);
+    if (threadIdx.x == 0) out[s] = t;
+  }
+}
+
+// Stage 1 of the plane sum: a fixed number of blocks per plane, each summing a
+// fixed contiguous chunk; NaN entries (pairs the reference raises on) skipped.
+constexpr int kPlaneBlocks = 256;
+
+__global__ void __launch_bounds__(kSumThreads)
+plane_partial_kernel(const float* __restrict__ values, int64_t plane_len,
+                     double* __restrict__ partial) {
+  const int plane = blockIdx.y;
+  const float* v = values + static_cast<int64_t>(plane) * plane_len;
+  const int64_t chunk = (plane_len + kPlaneBlocks - 1) / kPlaneBlocks;
+  const int64_t lo = static_cast<int64_t>(blockIdx.x) * chunk;
+  const int64_t hi = lo + chunk < plane_len ? lo + chunk : plane_len;
+  double acc = 0.0;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += kSumThreads) {
+    const float x = v[i];
+    if (x == x) acc += static_cast<double>(x);
+  }
+  const double t = block_sum(acc);
+  if (threadIdx.x == 0) partial[plane * kPlaneBlocks + blockIdx.x] = t;
+}
+
+__global__ void __launch_bounds__(kSumThreads)
+plane_final_kernel(const double* __restrict__ partial, double* __restrict__ out) {
+  const int plane = blockIdx.x;
+  const double v = threadIdx.x < kPlaneBlocks ? partial[plane * kPlaneBlocks + threadIdx.x] : 0.0;
+  const double t = block_sum(v);
+  if (threadIdx.x == 0) out[plane] = t;
+}
+
+__global__ void __launch_bounds__(256)
+special_scale_kernel(const float* __restrict__ run_time_ms, const float* __restrict__ pred_dest,
+                     const float* __restrict__ pred_orig, int64_t n, float* __restrict__ out_ms,
+                     uint32_t* __restrict__ negative_count) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  bool neg = false;
+  if (i < n) {
+    // predictor.py:182: run_time_ms * pred_dest / pred_orig, left to right
+    // (float64 there; the two predictions are float32 values)
+    double v = static_cast<double>(run_time_ms[i]) * static_cast<double>(pred_dest[i]) /
+               static_cast<double>(pred_orig[i]);
+    neg = v < 0;
+    if (neg) v = 0.0;  // predictor.py:135-141
+    out_ms[i] = static_cast<float>(v);
+  }
+  if (negative_count) {
+    const unsigned m = __ballot_sync(0xFFFFFFFFu, neg);
+    if ((threadIdx.x & 31) == 0 && m) atomicAdd(negative_count, __popc(m));
+  }
+}
+
+// Scratch for the plane sum's partials, grown on demand per process.
+double* g_partial = nullptr;
+size_t g_partial_planes = 0;
+
+}  // namespace
+
+extern "C" hb_status hb_segment_sum(const float* values, const int64_t* offsets,
+                                    int64_t n_segments, double* out, void* stream) {
+  if (n_segments < 0 || (n_segments > 0 && (!values || !offsets || !out))) {
+    hb::set_error("hb_segment_sum: bad arguments");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  if (n_segments == 0) return HB_OK;
+  const int64_t blocks = n_segments < 148 * 8 * 8 ? n_segments : 148 * 8 * 8;
+  segment_sum_kernel<<<static_cast<unsigned>(blocks), kSumThreads, 0,
+                       static_cast<cudaStream_t>(stream)>>>(values, offsets, n_segments, out);
+  HB_CUDA_TRY(cudaGetLastError());
+  return HB_OK;
+}
+
+extern "C" hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_t n_planes,
+                                  double* out, void* stream) {
+  if (plane_len < 0 || n_planes < 0 || n_planes > 65535 || (n_planes > 0 && (!values || !out))) {
+    hb::set_error("hb_plane_sum: bad arguments");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  if (n_planes == 0) return HB_OK;
+  if (static_cast<size_t>(n_planes) > g_partial_planes) {
+    if (g_partial) cudaFree(g_partial);
+    g_partial = nullptr;
+    g_partial_planes = 0;
+    HB_CUDA_TRY(cudaMalloc(&g_partial, sizeof(double) * kPlaneBlocks * n_planes));
+    g_partial_planes = n_planes;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  plane_partial_kernel<<<dim3(kPlaneBlocks, n_planes), kSumThreads, 0, s>>>(values, plane_len,
+                                                                            g_partial);
+  HB_CUDA_TRY(cudaGetLastError());
+  plane_final_kernel<<<n_planes, kSumThreads, 0, s>>>(g_partial, out);
+  HB_CUDA_TRY(cudaGetLastError());
+  return HB_OK;
+}
+
+extern "C" hb_status hb_special_scale(const float* run_time_ms, const float* pred_dest,
+                                      const float* pred_orig, int64_t n, float* out_ms,
+                                      uint32_t* negative_count, void* stream) {
+  if (n < 0 || (n > 0 && (!run_time_ms || !pred_dest || !pred_orig || !out_ms))) {
+    hb::set_error("hb_special_scale: bad arguments");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  if (n == 0) return HB_OK;
+  const int64_t blocks = (n + 255) / 256;
+  special_scale_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                         static_cast<cudaStream_t>(stream)>>>(run_time_ms, pred_dest, pred_orig, n,
+                                                              out_ms, negative_count);
+  HB_CUDA_TRY(cudaGetLastError());
+  return HB_OK;
+}

@@ -1,0 +1,468 @@
+// Wave scaling of recorded kernels: one fused elementwise kernel over
+// (kernel x destination-device) pairs.
+//
+// Stands in for the per-kernel Python loop of the reference
+// (analyzer/habitat/analysis/predictor.py:111-130 calling
+// wave_scaling/roofline.py:8-65, resimplified.py:7-40, common.py:3-20 and,
+// through pybind, cpp/src/cuda/kernel.cpp:33-56).
+//
+// Layout: kernels arrive as structure-of-arrays, results leave as
+// destination-major planes.  One thread owns VEC consecutive kernels and walks
+// all D destinations, so each record is read once and the origin-side
+// occupancy is computed once.  Device rows live in constant memory; the
+// per-launch (origin, destination) log2 ratios travel as a kernel parameter.
+// The kernel is HBM-bound by design: 20 B read + 5 B written per kernel and
+// 9 B written per pair.
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "hb_common.h"
+#include "occupancy.cuh"
+
+namespace {
+
+__constant__ hb_dev_pre c_dev[HB_MAX_DEVICES];
+
+// Host mirror of the uploaded table (ratios are formed from the raw rows).
+hb_device_spec g_rows[HB_MAX_DEVICES];
+hb_dev_pre g_pre[HB_MAX_DEVICES];
+int g_n_rows = 0;
+
+struct LaunchParams {
+  int32_t D;
+  int32_t origin_row;
+  int64_t K;
+  double origin_peak;          // origin peak GFLOP/s (metrics mode)
+  uint8_t dest_row[HB_MAX_DEVICES];
+  // large branch: log2 t' = log2 t + gamma * a + b, a = log2(bw) - b,
+  // b = log2(clock ratio) + log2(SM ratio); small branch uses log2_clk.
+  double a[HB_MAX_DEVICES];
+  double b[HB_MAX_DEVICES];
+  double log2_clk[HB_MAX_DEVICES];
+  double ridge[HB_MAX_DEVICES];  // destination peak / bandwidth (metrics mode)
+};
+
+// log2(i) for the per-SM block counts of the small-kernel branch (<= 32
+// because occupancy never exceeds the blocks-per-SM limit).
+__constant__ double c_log2_int[65];
+
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Vec {
+  T v[N];
+};
+
+template <typename T, int N>
+__device__ __forceinline__ Vec<T, N> load_vec(const T* p) {
+  return *reinterpret_cast<const Vec<T, N>*>(p);
+}
+template <typename T, int N>
+__device__ __forceinline__ void store_vec(T* p, const Vec<T, N>& v) {
+  *reinterpret_cast<Vec<T, N>*>(p) = v;
+}
+
+struct Ptrs {
+  const int32_t* num_blocks;
+  const uint16_t* block_size;
+  const uint16_t* regs;
+  const uint32_t* smem;
+  const float* time_ns;
+  const float* gamma;
+  const double* flop_eff;
+  const double* dram_read;
+  const double* dram_write;
+  const uint8_t* has_metrics;
+  const int16_t* dest_regs;
+  float* scaled_ns;
+  uint8_t* dest_occ;
+  uint32_t* dest_waves;
+  uint8_t* origin_occ;
+  uint32_t* origin_waves;
+  uint8_t* status;
+  int32_t* limits;
+};
+
+// Per-SM block count ceil(nb / sms) for a kernel that fits in one wave.
+__device__ __forceinline__ int32_t ceil_div_sms(int32_t nb, int32_t sms) {
+  return hb_div_small(nb + sms - 1, sms);
+}
+
+template <int VEC, bool METRICS, bool EXTRA>
+__global__ void __launch_bounds__(256)
+wave_scale_kernel(const Ptrs p, const __grid_constant__ LaunchParams lp) {
+  const int64_t K = lp.K;
+  const int64_t k0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
+  if (k0 >= K) return;
+
+  const Vec<int32_t, VEC> nbv = load_vec<int32_t, VEC>(p.num_blocks + k0);
+  const Vec<uint16_t, VEC> bsv = load_vec<uint16_t, VEC>(p.block_size + k0);
+  const Vec<uint16_t, VEC> rgv = load_vec<uint16_t, VEC>(p.regs + k0);
+  const Vec<uint32_t, VEC> smv = load_vec<uint32_t, VEC>(p.smem + k0);
+  const Vec<float, VEC> tv = load_vec<float, VEC>(p.time_ns + k0);
+  Vec<float, VEC> gv;
+  if (!METRICS) gv = load_vec<float, VEC>(p.gamma + k0);
+
+  const hb_dev_pre& od = c_dev[lp.origin_row];
+
+  int32_t smem[VEC], wave_o[VEC], omax[VEC];
+  double intensity[VEC];   // METRICS: GFLOP per GB, < 0 encodes the special cases
+  Vec<uint8_t, VEC> oocc;
+  Vec<uint32_t, VEC> owav;
+  int32_t lim[4];
+
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    smem[i] = smv.v[i] > 0x7FFF0000u ? -1 : static_cast<int32_t>(smv.v[i]);
+    const int32_t occ = hb_occupancy(od, bsv.v[i], smem[i], rgv.v[i], lim);
+    if (EXTRA && p.limits) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) p.limits[static_cast<int64_t>(j) * K + k0 + i] = lim[j];
+    }
+    wave_o[i] = od.num_sms * occ;
+    oocc.v[i] = static_cast<uint8_t>(occ);
+    const int32_t nb = nbv.v[i];
+    owav.v[i] = (wave_o[i] > 0 && nb >= 1) ? static_cast<uint32_t>(nb / wave_o[i]) : 0xFFFFFFFFu;
+    // only consulted when nb < wave_o, i.e. the value is <= occ <= 32
+    omax[i] = (nb >= 1 && nb < wave_o[i]) ? ceil_div_sms(nb, od.num_sms) : 1;
+    if (METRICS) {
+      // wave_scaling/roofline.py:68-88, same operation order, fp64
+      double g = -1.0;  // "no metrics": gamma = 1
+      if (p.has_metrics[k0 + i]) {
+        const double total_gb =
+            (p.dram_read[k0 + i] + p.dram_write[k0 + i]) / 1024 / 1024 / 1024;
+        const double gps = p.flop_eff[k0 + i] / 100 * lp.origin_peak;
+        const double gf = gps * static_cast<double>(tv.v[i]) / 1e9;
+        if (gf < 1e-9) g = -1.0;             // gamma = 1
+        else if (total_gb == 0) g = -2.0;    // gamma = 0
+        else g = gf / total_gb;
+      }
+      intensity[i] = g;
+    }
+  }
+  store_vec<uint8_t, VEC>(p.origin_occ + k0, oocc);
+  store_vec<uint32_t, VEC>(p.origin_waves + k0, owav);
+
+  for (int d = 0; d < lp.D; ++d) {
+    const hb_dev_pre& dd = c_dev[lp.dest_row[d]];
+    const int64_t base = static_cast<int64_t>(d) * K + k0;
+    Vec<float, VEC> outv;
+    Vec<uint8_t, VEC> occv, stv;
+    Vec<uint32_t, VEC> wavv;
+    Vec<int16_t, VEC> drv;
+    if (p.dest_regs) drv = load_vec<int16_t, VEC>(p.dest_regs + base);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int32_t nb = nbv.v[i];
+      int32_t regs = rgv.v[i];
+      if (p.dest_regs && drv.v[i] >= 0) regs = drv.v[i];
+      const int32_t occ = hb_occupancy(dd, bsv.v[i], smem[i], regs, lim);
+      if (EXTRA && p.limits) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          p.limits[(static_cast<int64_t>(d + 1) * 4 + j) * K + k0 + i] = lim[j];
+      }
+      const int32_t wave_d = dd.num_sms * occ;
+      occv.v[i] = static_cast<uint8_t>(occ);
+      wavv.v[i] = (wave_d > 0 && nb >= 1) ? static_cast<uint32_t>(nb / wave_d) : 0xFFFFFFFFu;
+
+      double gamma;
+      if (METRICS) {
+        const double x = intensity[i];
+        if (x == -1.0) gamma = 1.0;
+        else if (x == -2.0) gamma = 0.0;
+        else {
+          const double r = lp.ridge[d];
+          gamma = x > r ? 0.5 * r / x : -0.5 / r * x + 1.0;
+        }
+      } else {
+        gamma = static_cast<double>(gv.v[i]);
+      }
+
+      // Mirrors the short-circuit of roofline.py:29-30: the destination wave
+      // size is only examined when the kernel fits in one origin wave.
+      int32_t st;
+      double e = 0.0;  // log2 of the scale factor
+      if (nb < 1) {
+        st = HB_PAIR_BAD_INPUT;
+      } else if (wave_o[i] == 0) {
+        st = HB_PAIR_ZERO_WAVE;
+      } else if (nb < wave_o[i]) {
+        if (wave_d == 0) {
+          st = HB_PAIR_ZERO_WAVE;
+        } else if (nb < wave_d) {
+          st = HB_PAIR_SMALL;
+          const int32_t dmax = ceil_div_sms(nb, dd.num_sms);
+          e = (1.0 - gamma) * (lp.log2_clk[d] + c_log2_int[dmax] - c_log2_int[omax[i]]);
+        } else {
+          st = HB_PAIR_LARGE;
+        }
+      } else {
+        st = HB_PAIR_LARGE;
+      }
+      if (st == HB_PAIR_LARGE) e = fma(gamma, lp.a[d], lp.b[d]);
+      outv.v[i] = st <= HB_PAIR_SMALL ? tv.v[i] * exp2f(static_cast<float>(e))
+                                      : __int_as_float(0x7FC00000);
+      stv.v[i] = static_cast<uint8_t>(st);
+    }
+    store_vec<float, VEC>(p.scaled_ns + base, outv);
+    store_vec<uint8_t, VEC>(p.dest_occ + base, occv);
+    store_vec<uint32_t, VEC>(p.dest_waves + base, wavv);
+    if (EXTRA && p.status) store_vec<uint8_t, VEC>(p.status + base, stv);
+  }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <bool METRICS>
+hb_status launch(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream) {
+  const int64_t K = lp.K;
+  const bool extra = p.status != nullptr || p.limits != nullptr;
+  // The 4-wide path needs every plane base (d * K elements in) and every input
+  // to sit on a 16-byte boundary for its widest type.
+  const bool vec4 = (K % 4 == 0) && aligned16(p.num_blocks) && aligned16(p.smem) &&
+                    aligned16(p.time_ns) && (METRICS || aligned16(p.gamma)) &&
+                    aligned16(p.scaled_ns) && aligned16(p.dest_waves) &&
+                    aligned16(p.origin_waves) &&
+                    (reinterpret_cast<uintptr_t>(p.block_size) % 8 == 0) &&
+                    (reinterpret_cast<uintptr_t>(p.regs) % 8 == 0) &&
+                    (reinterpret_cast<uintptr_t>(p.dest_occ) % 4 == 0) &&
+                    (reinterpret_cast<uintptr_t>(p.origin_occ) % 4 == 0) &&
+                    (!p.status || reinterpret_cast<uintptr_t>(p.status) % 4 == 0) &&
+                    (!p.dest_regs || reinterpret_cast<uintptr_t>(p.dest_regs) % 8 == 0);
+  const int threads = 256;
+  const int vec = vec4 ? 4 : 1;
+  const int64_t nthreads = (K + vec - 1) / vec;
+  const int64_t blocks = (nthreads + threads - 1) / threads;
+  if (blocks > 0x7FFFFFFF) {
+    hb::set_error("hb_wave_scale: K too large for one launch");
+    return HB_ERR_TOO_LARGE;
+  }
+  const dim3 grid(static_cast<unsigned>(blocks));
+  if (vec4) {
+    if (extra) wave_scale_kernel<4, METRICS, true><<<grid, threads, 0, stream>>>(p, lp);
+    else wave_scale_kernel<4, METRICS, false><<<grid, threads, 0, stream>>>(p, lp);
+  } else {
+    if (extra) wave_scale_kernel<1, METRICS, true><<<grid, threads, 0, stream>>>(p, lp);
+    else wave_scale_kernel<1, METRICS, false><<<grid, threads, 0, stream>>>(p, lp);
+  }
+  HB_CUDA_TRY(cudaGetLastError());
+  return HB_OK;
+}
+
+hb_status fill_params(LaunchParams* lp, int64_t K, int32_t origin_row, const int32_t* dest_rows,
+                      int32_t D) {
+  if (g_n_rows == 0) {
+    hb::set_error("hb_wave_scale: no device table (call hb_set_devices first)");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  if (K < 0 || D < 1 || D > HB_MAX_DEVICES || !dest_rows || origin_row < 0 ||
+      origin_row >= g_n_rows) {
+    hb::set_error("hb_wave_scale: bad K/D/origin_row");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  std::memset(lp, 0, sizeof(*lp));
+  lp->D = D;
+  lp->K = K;
+  lp->origin_row = origin_row;
+  const hb_device_spec& o = g_rows[origin_row];
+  lp->origin_peak = static_cast<double>(o.peak_gflops_per_second);
+  for (int d = 0; d < D; ++d) {
+    const int r = dest_rows[d];
+    if (r < 0 || r >= g_n_rows) {
+      hb::set_error("hb_wave_scale: destination row %d out of range", r);
+      return HB_ERR_INVALID_ARGUMENT;
+    }
+    const hb_device_spec& t = g_rows[r];
+    lp->dest_row[d] = static_cast<uint8_t>(r);
+    // wave_scaling/roofline.py:48-57: ratios of the integer device fields
+    const double l_bw = std::log2(static_cast<double>(o.mem_bandwidth_gb) / t.mem_bandwidth_gb);
+    const double l_clk = std::log2(static_cast<double>(o.base_clock_mhz) / t.base_clock_mhz);
+    const double l_sm = std::log2(static_cast<double>(o.num_sms) / t.num_sms);
+    lp->b[d] = l_clk + l_sm;
+    lp->a[d] = l_bw - lp->b[d];
+    lp->log2_clk[d] = l_clk;
+    lp->ridge[d] = static_cast<double>(t.peak_gflops_per_second) / t.mem_bandwidth_gb;
+  }
+  return HB_OK;
+}
+
+hb_status check_io(const hb_kernel_soa* k, const hb_wave_out* out, bool need_gamma) {
+  if (!k || !out || !k->num_blocks || !k->block_size || !k->regs_per_thread || !k->smem_bytes ||
+      !k->run_time_ns || (need_gamma && !k->gamma) || !out->scaled_ns || !out->dest_occupancy ||
+      !out->dest_waves || !out->origin_occupancy || !out->origin_waves) {
+    hb::set_error("hb_wave_scale: required pointer is NULL");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  return HB_OK;
+}
+
+Ptrs make_ptrs(const hb_kernel_soa* k, const hb_kernel_metrics* m, const int16_t* dest_regs,
+               const hb_wave_out* out) {
+  Ptrs p{};
+  p.num_blocks = k->num_blocks;
+  p.block_size = k->block_size;
+  p.regs = k->regs_per_thread;
+  p.smem = k->smem_bytes;
+  p.time_ns = k->run_time_ns;
+  p.gamma = k->gamma;
+  if (m) {
+    p.flop_eff = m->flop_efficiency_pct;
+    p.dram_read = m->dram_read_bytes;
+    p.dram_write = m->dram_write_bytes;
+    p.has_metrics = m->has_metrics;
+  }
+  p.dest_regs = dest_regs;
+  p.scaled_ns = out->scaled_ns;
+  p.dest_occ = out->dest_occupancy;
+  p.dest_waves = out->dest_waves;
+  p.origin_occ = out->origin_occupancy;
+  p.origin_waves = out->origin_waves;
+  p.status = out->status;
+  p.limits = out->limits;
+  return p;
+}
+
+}  // namespace
+
+extern "C" hb_status hb_set_devices(const hb_device_spec* rows, int32_t n) {
+  if (!rows || n < 1 || n > HB_MAX_DEVICES) {
+    hb::set_error("hb_set_devices: need 1..%d rows", HB_MAX_DEVICES);
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  for (int i = 0; i < n; ++i) {
+    if (rows[i].mem_bandwidth_gb <= 0 || rows[i].base_clock_mhz <= 0 || rows[i].num_sms <= 0 ||
+        rows[i].peak_gflops_per_second <= 0) {
+      hb::set_error("hb_set_devices: row %d has a non-positive bandwidth/clock/SM/peak field", i);
+      return HB_ERR_INVALID_ARGUMENT;
+    }
+    g_rows[i] = rows[i];
+    g_pre[i] = hb_fold_device(rows[i]);
+  }
+  g_n_rows = n;
+  HB_CUDA_TRY(cudaMemcpyToSymbol(c_dev, g_pre, sizeof(hb_dev_pre) * n));
+  double lg[65];
+  lg[0] = 0.0;
+  for (int i = 1; i <= 64; ++i) lg[i] = std::log2(static_cast<double>(i));
+  HB_CUDA_TRY(cudaMemcpyToSymbol(c_log2_int, lg, sizeof(lg)));
+  return HB_OK;
+}
+
+extern "C" hb_status hb_wave_scale(const hb_kernel_soa* kernels, int64_t K, int32_t origin_row,
+                                   const int32_t* dest_rows_host, int32_t D,
+                                   const int16_t* dest_regs, const hb_wave_out* out,
+                                   void* stream) {
+  hb_status st = check_io(kernels, out, true);
+  if (st != HB_OK) return st;
+  LaunchParams lp;
+  st = fill_params(&lp, K, origin_row, dest_rows_host, D);
+  if (st != HB_OK) return st;
+  if (K == 0) return HB_OK;
+  return launch<false>(make_ptrs(kernels, nullptr, dest_regs, out), lp,
+                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" hb_status hb_wave_scale_metrics(const hb_kernel_soa* kernels,
+                                           const hb_kernel_metrics* metrics, int64_t K,
+                                           int32_t origin_row, const int32_t* dest_rows_host,
+                                           int32_t D, const int16_t* dest_regs,
+                                           const hb_wave_out* out, void* stream) {
+  hb_status st = check_io(kernels, out, false);
+  if (st != HB_OK) return st;
+  if (!metrics || !metrics->flop_efficiency_pct || !metrics->dram_read_bytes ||
+      !metrics->dram_write_bytes || !metrics->has_metrics) {
+    hb::set_error("hb_wave_scale_metrics: metrics pointer is NULL");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  LaunchParams lp;
+  st = fill_params(&lp, K, origin_row, dest_rows_host, D);
+  if (st != HB_OK) return st;
+  if (K == 0) return HB_OK;
+  return launch<true>(make_ptrs(kernels, metrics, dest_regs, out), lp,
+                      static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+
+// Scoped device buffer for the host-buffer entry points.
+struct DevBuf {
+  void* p = nullptr;
+  ~DevBuf() { if (p) cudaFree(p); }
+  cudaError_t alloc(size_t n) { return cudaMalloc(&p, n ? n : 1); }
+  template <typename T> T* as() { return static_cast<T*>(p); }
+};
+
+}  // namespace
+
+extern "C" hb_status hb_wave_scale_host(const hb_kernel_soa* kernels, int64_t K,
+                                        int32_t origin_row, const int32_t* dest_rows_host,
+                                        int32_t D, const int16_t* dest_regs,
+                                        const hb_wave_out* out) {
+  hb_status st = check_io(kernels, out, true);
+  if (st != HB_OK) return st;
+  LaunchParams lp;
+  st = fill_params(&lp, K, origin_row, dest_rows_host, D);
+  if (st != HB_OK) return st;
+  if (K == 0) return HB_OK;
+  const size_t k = static_cast<size_t>(K), kd = k * D;
+  cudaStream_t s = nullptr;
+  DevBuf nb, bs, rg, sm, tm, gm, dr, o_ns, o_occ, o_wav, o_oocc, o_owav, o_st, o_lim;
+  HB_CUDA_TRY(nb.alloc(k * 4)); HB_CUDA_TRY(bs.alloc(k * 2)); HB_CUDA_TRY(rg.alloc(k * 2));
+  HB_CUDA_TRY(sm.alloc(k * 4)); HB_CUDA_TRY(tm.alloc(k * 4)); HB_CUDA_TRY(gm.alloc(k * 4));
+  HB_CUDA_TRY(o_ns.alloc(kd * 4)); HB_CUDA_TRY(o_occ.alloc(kd)); HB_CUDA_TRY(o_wav.alloc(kd * 4));
+  HB_CUDA_TRY(o_oocc.alloc(k)); HB_CUDA_TRY(o_owav.alloc(k * 4));
+  if (dest_regs) HB_CUDA_TRY(dr.alloc(kd * 2));
+  if (out->status) HB_CUDA_TRY(o_st.alloc(kd));
+  if (out->limits) HB_CUDA_TRY(o_lim.alloc(static_cast<size_t>(D + 1) * 4 * k * 4));
+  const cudaMemcpyKind h2d = cudaMemcpyHostToDevice, d2h = cudaMemcpyDeviceToHost;
+  HB_CUDA_TRY(cudaMemcpyAsync(nb.p, kernels->num_blocks, k * 4, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(bs.p, kernels->block_size, k * 2, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(rg.p, kernels->regs_per_thread, k * 2, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(sm.p, kernels->smem_bytes, k * 4, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(tm.p, kernels->run_time_ns, k * 4, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(gm.p, kernels->gamma, k * 4, h2d, s));
+  if (dest_regs) HB_CUDA_TRY(cudaMemcpyAsync(dr.p, dest_regs, kd * 2, h2d, s));
+  hb_kernel_soa dk{nb.as<int32_t>(), bs.as<uint16_t>(), rg.as<uint16_t>(), sm.as<uint32_t>(),
+                   tm.as<float>(), gm.as<float>()};
+  hb_wave_out dout{o_ns.as<float>(), o_occ.as<uint8_t>(), o_wav.as<uint32_t>(),
+                   o_oocc.as<uint8_t>(), o_owav.as<uint32_t>(),
+                   out->status ? o_st.as<uint8_t>() : nullptr,
+                   out->limits ? o_lim.as<int32_t>() : nullptr};
+  st = launch<false>(make_ptrs(&dk, nullptr, dest_regs ? dr.as<int16_t>() : nullptr, &dout), lp, s);
+  if (st != HB_OK) return st;
+  HB_CUDA_TRY(cudaMemcpyAsync(out->scaled_ns, o_ns.p, kd * 4, d2h, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(out->dest_occupancy, o_occ.p, kd, d2h, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(out->dest_waves, o_wav.p, kd * 4, d2h, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(out->origin_occupancy, o_oocc.p, k, d2h, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(out->origin_waves, o_owav.p, k * 4, d2h, s));
+  if (out->status) HB_CUDA_TRY(cudaMemcpyAsync(out->status, o_st.p, kd, d2h, s));
+  if (out->limits)
+    HB_CUDA_TRY(cudaMemcpyAsync(out->limits, o_lim.p, static_cast<size_t>(D + 1) * 4 * k * 4, d2h, s));
+  HB_CUDA_TRY(cudaStreamSynchronize(s));
+  return HB_OK;
+}
+
+extern "C" hb_status hb_thread_block_occupancy(int32_t device_row, int32_t block_size,
+                                               uint32_t smem_bytes, int32_t regs_per_thread,
+                                               int32_t* occupancy, int32_t limits[4]) {
+  if (!occupancy || block_size < 0 || block_size > 0xFFFF || regs_per_thread < 0 ||
+      regs_per_thread > 0xFFFF) {
+    hb::set_error("hb_thread_block_occupancy: argument out of range");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  // One record through the batched kernel, with the queried row as origin.
+  int32_t nb = 1;
+  uint16_t bs = static_cast<uint16_t>(block_size), rg = static_cast<uint16_t>(regs_per_thread);
+  float t = 1.0f, g = 1.0f;
+  hb_kernel_soa k{&nb, &bs, &rg, &smem_bytes, &t, &g};
+  float ns;
+  uint8_t docc, oocc;
+  uint32_t dw, ow;
+  int32_t lim[8];
+  hb_wave_out out{&ns, &docc, &dw, &oocc, &ow, nullptr, lim};
+  const int32_t dest = device_row;
+  hb_status st = hb_wave_scale_host(&k, 1, device_row, &dest, 1, nullptr, &out);
+  if (st != HB_OK) return st;
+  *occupancy = oocc;
+  if (limits) for (int j = 0; j < 4; ++j) limits[j] = lim[j];
+  return HB_OK;
+}

@@ -1,0 +1,232 @@
+/*
+ * habitat_b200 -- C ABI of the B200 (sm_100a) batched prediction library.
+ *
+ * Every entry point takes plain pointers and sizes, returns an hb_status and
+ * never throws or aborts.  Unless an entry point's name ends in `_host`, its
+ * data pointers are DEVICE pointers owned by the caller, the work is queued on
+ * the caller's CUDA stream (passed as an opaque `void*` cudaStream_t; NULL is
+ * the default stream) and the call does not synchronise.  `_host` entry
+ * points take host buffers, do their own transfers and return when the result
+ * is in the caller's buffer.
+ *
+ * Each declaration cites the reference interface it stands in for (paths are
+ * relative to the geoffxy/habitat tree).
+ */
+#ifndef HABITAT_B200_H
+#define HABITAT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t hb_status;
+enum {
+  HB_OK = 0,
+  HB_ERR_INVALID_ARGUMENT = 1,
+  HB_ERR_CUDA = 2,          /* a CUDA runtime call failed; see hb_last_error() */
+  HB_ERR_UNSUPPORTED = 3,   /* shape outside what the kernels handle          */
+  HB_ERR_DEVICE_TIMEOUT = 4,/* a bounded device-side wait ran out             */
+  HB_ERR_TOO_LARGE = 5      /* size beyond a fixed-capacity entry point       */
+};
+
+/* Text of the most recent error on the calling thread ("" if none). */
+const char* hb_last_error(void);
+
+/* Library version, "major.minor.patch". */
+const char* hb_version(void);
+
+/* ------------------------------------------------------------------------ */
+/* Device table                                                             */
+/* ------------------------------------------------------------------------ */
+
+#define HB_MAX_DEVICES 64
+
+/* Numeric fields of habitat::cuda::DeviceProperties
+ * (cpp/src/cuda/kernel.h:14-62; bound at cpp/src/frontend/model_bindings.cpp:17-55)
+ * plus the driver-reserved shared memory per block used for compute
+ * capability >= 8 (0 otherwise). */
+typedef struct {
+  int32_t compute_major;
+  int32_t compute_minor;
+  int32_t max_threads_per_block;
+  int32_t max_threads_per_multiprocessor;
+  int32_t regs_per_block;
+  int32_t regs_per_multiprocessor;
+  int32_t warp_size;
+  int32_t shared_mem_per_block;
+  int32_t shared_mem_per_multiprocessor;
+  int32_t num_sms;
+  int32_t shared_mem_per_block_optin;
+  int32_t reserved_shared_mem_per_block;
+  int32_t mem_bandwidth_gb;
+  int32_t base_clock_mhz;
+  int32_t peak_gflops_per_second;
+} hb_device_spec;
+
+/* Replaces the per-call `hc.DeviceProperties` arguments of
+ * KernelInstance.thread_block_occupancy (cpp/src/frontend/model_bindings.cpp:75-82):
+ * rows are uploaded once to constant memory of the current CUDA device and
+ * referred to by index afterwards.  n <= HB_MAX_DEVICES.  Synchronous. */
+hb_status hb_set_devices(const hb_device_spec* rows, int32_t n);
+
+/* ------------------------------------------------------------------------ */
+/* Wave scaling                                                             */
+/* ------------------------------------------------------------------------ */
+
+/* Structure-of-arrays view of K recorded kernels: the fields of
+ * habitat::cuda::KernelMetadata / KernelInstance (cpp/src/cuda/kernel.h:64-151)
+ * that the prediction path reads.  smem_bytes is static + dynamic shared
+ * memory (only the sum enters the occupancy calculation under Habitat's call
+ * convention, cpp/src/cuda/kernel.cpp:37-51).  gamma is the memory-bound
+ * fraction of wave_scaling/roofline.py:14; pass gamma = 1 for kernels without
+ * metrics (that is wave_scaling/resimplified.py:7-40). */
+typedef struct {
+  const int32_t* num_blocks;      /* [K] >= 1                      */
+  const uint16_t* block_size;     /* [K] threads per block         */
+  const uint16_t* regs_per_thread;/* [K]                           */
+  const uint32_t* smem_bytes;     /* [K] static + dynamic          */
+  const float* run_time_ns;       /* [K] measured time             */
+  const float* gamma;             /* [K] in [0, 1]                 */
+} hb_kernel_soa;
+
+/* Raw metrics form of gamma (wave_scaling/roofline.py:68-104): when passed to
+ * hb_wave_scale_metrics, gamma is computed per (kernel, destination) pair from
+ * these instead of being read from hb_kernel_soa.gamma.  has_metrics[k] == 0
+ * selects the no-metrics rule (gamma = 1, wave_scaling/unified.py:26-35). */
+typedef struct {
+  const double* flop_efficiency_pct; /* [K] Metric.SinglePrecisionFLOPEfficiency */
+  const double* dram_read_bytes;     /* [K] Metric.DRAMReadBytes                 */
+  const double* dram_write_bytes;    /* [K] Metric.DRAMWriteBytes                */
+  const uint8_t* has_metrics;        /* [K] all three present                    */
+} hb_kernel_metrics;
+
+/* Outputs.  Planes are destination-major: element (d, k) is at d*K + k.
+ * scaled_ns is NaN exactly where the Python reference would raise.  Any
+ * pointer from `status` down may be NULL to skip that output. */
+typedef struct {
+  float* scaled_ns;        /* [D][K] predicted time on destination d          */
+  uint8_t* dest_occupancy; /* [D][K] thread blocks per SM                     */
+  uint32_t* dest_waves;    /* [D][K] num_blocks // (num_sms * occupancy);
+                                     0xFFFFFFFF where the wave size is 0      */
+  uint8_t* origin_occupancy; /* [K]                                           */
+  uint32_t* origin_waves;    /* [K]                                           */
+  uint8_t* status;         /* [D][K] hb_pair_status                           */
+  int32_t* limits;         /* [(D+1)][4][K] block limits {regs, warps, blocks,
+                                     smem}; plane 0 is the origin             */
+} hb_wave_out;
+
+enum {
+  HB_PAIR_LARGE = 0,     /* wave_scaling/roofline.py:48-65                    */
+  HB_PAIR_SMALL = 1,     /* wave_scaling/roofline.py:29-45                    */
+  HB_PAIR_ZERO_WAVE = 2, /* the reference raises ZeroDivisionError            */
+  HB_PAIR_BAD_INPUT = 3  /* num_blocks < 1                                    */
+};
+
+/* Replaces the per-kernel loop of Predictor._wave_scale
+ * (analyzer/habitat/analysis/predictor.py:111-130) over
+ * roofline_wave_scaling / resimplified_wave_scaling
+ * (wave_scaling/roofline.py:8-65, resimplified.py:7-40) and
+ * calculate_wave_info (wave_scaling/common.py:3-20), for K kernels and D
+ * destination rows at once.  dest_regs ([D][K], may be NULL) carries the
+ * result of MetadataManager.kernel_registers_for (wave_scaling/metadata.py:12-37),
+ * -1 meaning "no entry: use the kernel's own register count". */
+hb_status hb_wave_scale(const hb_kernel_soa* kernels, int64_t K, int32_t origin_row,
+                        const int32_t* dest_rows_host, int32_t D,
+                        const int16_t* dest_regs, const hb_wave_out* out, void* stream);
+
+/* Same, with gamma computed on the device from raw metrics
+ * (wave_scaling/roofline.py:68-104, wave_scaling/unified.py:8-35). */
+hb_status hb_wave_scale_metrics(const hb_kernel_soa* kernels, const hb_kernel_metrics* metrics,
+                                int64_t K, int32_t origin_row, const int32_t* dest_rows_host,
+                                int32_t D, const int16_t* dest_regs, const hb_wave_out* out,
+                                void* stream);
+
+/* Host-buffer form of hb_wave_scale: all pointers in `kernels`, `dest_regs`
+ * and `out` are HOST pointers; transfers happen inside the call. */
+hb_status hb_wave_scale_host(const hb_kernel_soa* kernels, int64_t K, int32_t origin_row,
+                             const int32_t* dest_rows_host, int32_t D,
+                             const int16_t* dest_regs, const hb_wave_out* out);
+
+/* Single-kernel occupancy with the four block limits: the batched device
+ * path run on one record.  Stands in for
+ * KernelInstance.thread_block_occupancy(device, registers_per_thread)
+ * (cpp/src/frontend/model_bindings.cpp:75-82).  Host in/out, synchronous. */
+hb_status hb_thread_block_occupancy(int32_t device_row, int32_t block_size, uint32_t smem_bytes,
+                                    int32_t regs_per_thread, int32_t* occupancy,
+                                    int32_t limits[4]);
+
+/* ------------------------------------------------------------------------ */
+/* MLP runtime predictors                                                   */
+/* ------------------------------------------------------------------------ */
+
+typedef struct hb_mlp hb_mlp;
+
+enum { HB_PRECISION_BF16 = 0, HB_PRECISION_BF16X3 = 1 };
+
+/* Builds the device-side weight pack of one runtime predictor: the module
+ * RuntimePredictor owns (analyzer/habitat/analysis/mlp/mlp.py:113-131;
+ * topology mlp.py:17-109: fc1 (F+4 -> width) + ReLU, `layers` x [width ->
+ * width + ReLU], fc2 (width -> 1)) together with its mu/sigma
+ * (mlp.py:133-137).  All pointers are HOST pointers, weights row-major
+ * [out][in] as in torch.nn.Linear:
+ *   fc1_w [width][F+4], fc1_b [width], hidden_w [layers][width][width],
+ *   hidden_b [layers][width], fc2_w [width], fc2_b [1], mu/sigma [F+4].
+ * device_features is [n_device_rows][4] = (mem, mem_bw, num_sm, single), the
+ * columns RuntimePredictor.predict reads from devices.csv
+ * (analysis/mlp/devices.py:5-10, mlp.py:125).  width must be 1024. */
+hb_status hb_mlp_create(hb_mlp** handle, int32_t n_op_features, int32_t layers, int32_t width,
+                        const float* fc1_w, const float* fc1_b, const float* hidden_w,
+                        const float* hidden_b, const float* fc2_w, const float* fc2_b,
+                        const double* mu, const double* sigma, const double* device_features,
+                        int32_t n_device_rows, int32_t precision);
+
+void hb_mlp_destroy(hb_mlp* handle);
+
+/* Replaces RuntimePredictor.predict (analysis/mlp/mlp.py:252-267) for Q
+ * queries at once: op_features [Q][F] float32 row-major, device_row [Q]
+ * indexes device_features, out [Q] float32 (milliseconds, un-clamped). */
+hb_status hb_mlp_predict(hb_mlp* handle, const float* op_features, const uint8_t* device_row,
+                         int64_t Q, float* out, void* stream);
+
+/* Synchronises with the device and reports whether any launch on this handle
+ * gave up on a bounded device-side wait (HB_ERR_DEVICE_TIMEOUT; *device_status
+ * names the waiting role and site) since the handle was created.  No reference
+ * counterpart: the reference's predict() is host code. */
+hb_status hb_mlp_status(hb_mlp* handle, int32_t* device_status);
+
+/* Host-buffer form of hb_mlp_predict; also checks hb_mlp_status. */
+hb_status hb_mlp_predict_host(hb_mlp* handle, const float* op_features,
+                              const uint8_t* device_row, int64_t Q, float* out);
+
+/* Replaces the last line of Predictor._{conv2d,linear,bmm,lstm}_scale and the
+ * clamp of Predictor._special_scale (analysis/predictor.py:132-148, :182):
+ * out_ms[i] = max(0, run_time_ms[i] * pred_dest[i] / pred_orig[i]);
+ * *negative_count (device, may be NULL) is incremented per clamped value. */
+hb_status hb_special_scale(const float* run_time_ms, const float* pred_dest,
+                           const float* pred_orig, int64_t n, float* out_ms,
+                           uint32_t* negative_count, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Trace-level totals                                                       */
+/* ------------------------------------------------------------------------ */
+
+/* Replaces Trace.run_time_ms (analyzer/habitat/analysis/trace.py:26-36) and
+ * RunTimePrediction.run_time_ms (analysis/run_time.py:49-58) for many
+ * segments at once: out[s] = sum(values[offsets[s] : offsets[s+1]]) in
+ * float64, fixed summation order (results do not depend on the launch). */
+hb_status hb_segment_sum(const float* values, const int64_t* offsets, int64_t n_segments,
+                         double* out, void* stream);
+
+/* Sum of each of n_planes contiguous planes of plane_len float32 values,
+ * skipping NaN entries (pairs the reference would have raised on); used for
+ * per-destination totals of hb_wave_out.scaled_ns.  out [n_planes] float64. */
+hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_t n_planes, double* out,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
