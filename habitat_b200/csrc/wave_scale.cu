@@ -286,7 +286,8 @@ hb_status fill_params(LaunchParams* lp, int64_t K, int32_t origin_row, const int
   return HB_OK;
 }
 
-hb_status check_io(const hb_kernel_soa* k, const hb_wave_out* out, bool need_gamma) {
+hb_status check_io(const hb_kernel_soa* k, const hb_wave_out* out, bool need_gamma, int64_t K) {
+  if (K == 0 && k && out) return HB_OK;  // nothing to read or write: pointers may be NULL
   if (!k || !out || !k->num_blocks || !k->block_size || !k->regs_per_thread || !k->smem_bytes ||
       !k->run_time_ns || (need_gamma && !k->gamma) || !out->scaled_ns || !out->dest_occupancy ||
       !out->dest_waves || !out->origin_occupancy || !out->origin_waves) {
@@ -351,7 +352,7 @@ extern "C" hb_status hb_wave_scale(const hb_kernel_soa* kernels, int64_t K, int3
                                    const int32_t* dest_rows_host, int32_t D,
                                    const int16_t* dest_regs, const hb_wave_out* out,
                                    void* stream) {
-  hb_status st = check_io(kernels, out, true);
+  hb_status st = check_io(kernels, out, true, K);
   if (st != HB_OK) return st;
   LaunchParams lp;
   st = fill_params(&lp, K, origin_row, dest_rows_host, D);
@@ -366,10 +367,10 @@ extern "C" hb_status hb_wave_scale_metrics(const hb_kernel_soa* kernels,
                                            int32_t origin_row, const int32_t* dest_rows_host,
                                            int32_t D, const int16_t* dest_regs,
                                            const hb_wave_out* out, void* stream) {
-  hb_status st = check_io(kernels, out, false);
+  hb_status st = check_io(kernels, out, false, K);
   if (st != HB_OK) return st;
-  if (!metrics || !metrics->flop_efficiency_pct || !metrics->dram_read_bytes ||
-      !metrics->dram_write_bytes || !metrics->has_metrics) {
+  if (!metrics || (K > 0 && (!metrics->flop_efficiency_pct || !metrics->dram_read_bytes ||
+                             !metrics->dram_write_bytes || !metrics->has_metrics))) {
     hb::set_error("hb_wave_scale_metrics: metrics pointer is NULL");
     return HB_ERR_INVALID_ARGUMENT;
   }
@@ -397,7 +398,7 @@ extern "C" hb_status hb_wave_scale_host(const hb_kernel_soa* kernels, int64_t K,
                                         int32_t origin_row, const int32_t* dest_rows_host,
                                         int32_t D, const int16_t* dest_regs,
                                         const hb_wave_out* out) {
-  hb_status st = check_io(kernels, out, true);
+  hb_status st = check_io(kernels, out, true, K);
   if (st != HB_OK) return st;
   LaunchParams lp;
   st = fill_params(&lp, K, origin_row, dest_rows_host, D);

@@ -133,3 +133,19 @@ def init_mlp_weights(op, seed=None, layers=8, width=1024, gain=1.0):
     fc2_w, fc2_b = lin(1, width)
     return dict(fc1_w=fc1_w, fc1_b=fc1_b, hidden_w=np.stack(hw), hidden_b=np.stack(hb),
                 fc2_w=fc2_w.reshape(-1), fc2_b=fc2_b)
+
+
+def torch_init_mlp_weights(op, seed=None, layers=8, width=1024):
+    """Weights exactly as the reference creates them for a fresh predictor:
+    torch.manual_seed(seed) followed by the construction of the op's MLP class
+    (torch.nn.Linear default init, modules created in the order fc1, hidden
+    stack, fc2 as in analysis/mlp/mlp.py:34-50)."""
+    import torch
+    from habitat_b200.analysis.mlp.mlp import RuntimePredictor, state_to_arrays
+    state = torch.random.get_rng_state()
+    try:
+        torch.manual_seed(WEIGHT_SEED[op] if seed is None else seed)
+        pred = RuntimePredictor(op, layers, width)
+    finally:
+        torch.random.set_rng_state(state)
+    return state_to_arrays(pred.model)

@@ -1,0 +1,110 @@
+"""Fused MLP predictor kernel (through the C ABI) against the numpy oracle."""
+import numpy as np
+import pytest
+import torch
+
+from habitat_b200 import batched, workloads
+from oracle import mlp as omlp
+
+pytestmark = pytest.mark.gpu
+
+DEVF = workloads.BENCH_DEVICE_FEATURES
+
+
+def _run(op, Q, weights, precision, seed, mu_sigma=None):
+    feats, dev = workloads.make_queries(op, Q, seed)
+    mu, sigma = mu_sigma if mu_sigma is not None else workloads.batch_mu_sigma(feats, dev)
+    h = batched.MLPHandle(feats.shape[1], mu=mu, sigma=sigma, device_features=DEVF,
+                          precision=precision, **weights)
+    out = h.predict(torch.from_numpy(feats).cuda(), torch.from_numpy(dev).cuda())
+    torch.cuda.synchronize()
+    h.check_status()
+    got = out.cpu().numpy()
+    ref32 = omlp.predict(weights, feats, dev, DEVF, mu, sigma, np.float32)
+    ref64 = omlp.predict(weights, feats, dev, DEVF, mu, sigma, np.float64)
+    h.close()
+    return got, ref32, ref64
+
+
+def _rel(got, ref):
+    return np.abs(got.astype(np.float64) - ref) / np.abs(ref)
+
+
+@pytest.mark.parametrize("op", ["linear", "conv2d", "bmm", "lstm"])
+def test_bf16_reference_init(op):
+    """Weights as the reference initialises a fresh predictor; tolerance 2e-2
+    relative for the bf16 tensor-core path (float32 reference)."""
+    w = workloads.torch_init_mlp_weights(op)
+    got, ref32, ref64 = _run(op, 4096, w, "bf16", seed=1003)
+    assert np.isfinite(got).all()
+    assert _rel(got, ref32).max() <= 2e-2
+    print(op, "bf16 max rel", _rel(got, ref64).max())
+
+
+@pytest.mark.parametrize("Q", [1, 63, 64, 65, 127, 129, 4096 + 17])
+def test_tile_tails(Q):
+    w = workloads.torch_init_mlp_weights("conv2d")
+    feats, dev = workloads.make_queries("conv2d", 8192, 77)
+    mu_sigma = workloads.batch_mu_sigma(feats, dev)
+    got, ref32, _ = _run("conv2d", Q, w, "bf16", seed=77, mu_sigma=mu_sigma)
+    assert got.shape == (Q,)
+    assert _rel(got, ref32).max() <= 2e-2
+
+
+@pytest.mark.parametrize("op", ["linear", "conv2d"])
+def test_bf16_input_sensitive(op):
+    """Random-init predictors are nearly constant functions, so a kernel that
+    ignored its inputs would pass the case above.  Scaling fc1 and hidden
+    weights by sqrt(6) keeps the activation variance through the stack and makes
+    the output move with the input; errors are then judged against the spread
+    of the outputs (single-pass bf16: a few percent worst case)."""
+    w = workloads.init_mlp_weights(op, seed=11, gain=np.sqrt(6.0))
+    got, ref32, ref64 = _run(op, 4096, w, "bf16", seed=1004)
+    spread = ref64.std()
+    assert spread > 0.05 * np.abs(ref64).mean()          # the outputs do vary
+    err = np.abs(got - ref64)
+    assert err.max() <= 8e-2 * spread + 2e-2 * np.abs(ref64).max()
+    assert err.mean() <= 1e-2 * spread + 4e-3 * np.abs(ref64).mean()
+    assert np.corrcoef(got, ref64)[0, 1] > 0.999
+
+
+@pytest.mark.parametrize("op", ["linear", "lstm"])
+def test_split_precision_config1(op):
+    """hi/lo split path: 1e-4 relative against the float32 reference."""
+    w = workloads.torch_init_mlp_weights(op)
+    got, ref32, ref64 = _run(op, 2048 + 5, w, "bf16x3", seed=1001)
+    assert _rel(got, ref32).max() <= 1e-4
+    print(op, "bf16x3 max rel vs fp64", _rel(got, ref64).max())
+
+
+def test_split_precision_input_sensitive():
+    w = workloads.init_mlp_weights("linear", seed=12, gain=np.sqrt(6.0))
+    got, ref32, ref64 = _run("linear", 2048, w, "bf16x3", seed=1005)
+    err = np.abs(got - ref64)
+    assert err.max() <= 2e-4 * (ref64.std() + np.abs(ref64).max())
+
+
+def test_wide_sigma_and_negative_outputs():
+    """sigma spanning 1 .. 1e4 and a weight set whose outputs go negative."""
+    op = "conv2d"
+    w = workloads.init_mlp_weights(op, seed=13, gain=np.sqrt(6.0))
+    w["fc2_b"] = w["fc2_b"] - 0.5
+    feats, dev = workloads.make_queries(op, 4096, 1006)
+    mu, sigma = workloads.batch_mu_sigma(feats, dev)
+    sigma = sigma * np.logspace(0, 4, sigma.shape[0]) / sigma.max()
+    got, ref32, ref64 = _run(op, 4096, w, "bf16", seed=1006, mu_sigma=(mu, sigma))
+    assert (ref64 < 0).any()
+    err = np.abs(got - ref64)
+    assert err.max() <= 8e-2 * ref64.std() + 2e-2 * np.abs(ref64).max()
+
+
+def test_host_buffer_entry_point():
+    op = "bmm"
+    w = workloads.torch_init_mlp_weights(op)
+    feats, dev = workloads.make_queries(op, 1000, 5)
+    mu, sigma = workloads.batch_mu_sigma(feats, dev)
+    h = batched.MLPHandle(4, mu=mu, sigma=sigma, device_features=DEVF, **w)
+    got = h.predict_host(feats, dev)
+    ref = omlp.predict(w, feats, dev, DEVF, mu, sigma)
+    assert _rel(got, ref).max() <= 2e-2
+    h.close()
