@@ -1,0 +1,96 @@
+"""Flattening of recorded kernels into the structure-of-arrays the device path takes.
+
+This is the host half of wave scaling: it walks MeasuredKernel objects once,
+resolves metrics and per-destination register counts, and hands flat arrays to
+the fused kernel (habitat_b200/csrc/wave_scale.cu).  No scaling arithmetic
+happens here.
+"""
+import numpy as np
+import torch
+
+from habitat_b200 import batched
+from habitat_b200.analysis.metrics import Metric
+
+ROOFLINE, RESIMPLIFIED, UNIFIED = "roofline", "resimplified", "unified"
+
+_NEEDED = (Metric.SinglePrecisionFLOPEfficiency, Metric.DRAMReadBytes, Metric.DRAMWriteBytes)
+
+
+def flatten_kernels(kernels, mode):
+    """kernels: sequence of MeasuredKernel (or objects with the same surface).
+    Returns (arrays, metrics or None, names)."""
+    K = len(kernels)
+    nb = np.empty(K, np.int32)
+    bs = np.empty(K, np.uint16)
+    rg = np.empty(K, np.uint16)
+    sm = np.empty(K, np.uint32)
+    tm = np.empty(K, np.float64)
+    eff = np.zeros(K, np.float64)
+    rd = np.zeros(K, np.float64)
+    wr = np.zeros(K, np.float64)
+    has = np.zeros(K, np.uint8)
+    names = []
+    for i, k in enumerate(kernels):
+        md = k.metadata
+        nb[i] = k.num_blocks
+        bs[i] = min(max(int(md["block_size"]), 0), 0xFFFF)
+        rg[i] = int(md["registers_per_thread"]) & 0xFFFF
+        smem = int(md["static_shared_memory"]) + int(md["dynamic_shared_memory"])
+        sm[i] = smem if 0 <= smem <= 0xFFFFFFFF else 0xFFFFFFFF
+        tm[i] = k.run_time_ns
+        names.append(k.name)
+        if mode != RESIMPLIFIED:
+            try:
+                vals = [k.get_metric(m) for m in _NEEDED]
+            except AttributeError:
+                if mode == ROOFLINE:
+                    raise
+                continue
+            eff[i], rd[i], wr[i] = vals
+            has[i] = 1
+    arrays = dict(num_blocks=nb, block_size=bs, regs_per_thread=rg, smem_bytes=sm, run_time_ns=tm,
+                  gamma=np.ones(K, np.float32))
+    metrics = None
+    if mode != RESIMPLIFIED and has.any():
+        metrics = dict(flop_efficiency_pct=eff, dram_read_bytes=rd, dram_write_bytes=wr,
+                       has_metrics=has)
+    return arrays, metrics, names
+
+
+def scale_kernels(kernels, origin_device, dest_devices, metadata_manager, mode=UNIFIED):
+    """Runs the fused kernel for `kernels` x `dest_devices`.
+
+    Returns (result, device tensors kept alive): result is a WaveResult whose
+    tensors live on the GPU; nothing is synchronised here."""
+    arrays, metrics, names = flatten_kernels(kernels, mode)
+    kb = batched.KernelBatch.from_numpy(arrays)
+    mb = None
+    if metrics is not None:
+        mb = batched.KernelMetricsBatch(
+            torch.from_numpy(metrics["flop_efficiency_pct"]).cuda(),
+            torch.from_numpy(metrics["dram_read_bytes"]).cuda(),
+            torch.from_numpy(metrics["dram_write_bytes"]).cuda(),
+            torch.from_numpy(metrics["has_metrics"]).cuda())
+    dest_regs = None
+    if metadata_manager is not None and hasattr(metadata_manager, "registers_matrix"):
+        m = metadata_manager.registers_matrix(names, dest_devices)
+        if m is not None:
+            dest_regs = torch.from_numpy(m).cuda()
+    elif metadata_manager is not None:
+        # a foreign manager with only the per-kernel query of the reference
+        m = np.full((len(dest_devices), len(kernels)), -1, np.int16)
+        for d, dev in enumerate(dest_devices):
+            for i, k in enumerate(kernels):
+                r = metadata_manager.kernel_registers_for(k, dev)
+                if r is not None:
+                    m[d, i] = r
+        if (m >= 0).any():
+            dest_regs = torch.from_numpy(m).cuda()
+    return batched.wave_scale(kb, origin_device, dest_devices, dest_regs=dest_regs, metrics=mb,
+                              want_status=True)
+
+
+def raise_like_reference(status_host):
+    """The reference divides by a zero wave size for these pairs."""
+    if (status_host >= 2).any():
+        raise ZeroDivisionError("integer division or modulo by zero")

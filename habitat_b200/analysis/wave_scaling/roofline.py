@@ -1,0 +1,20 @@
+"""roofline wave scaling of a single kernel.
+
+Reference: analyzer/habitat/analysis/wave_scaling/roofline.py.  Same call signature
+(a wave-scaling strategy is any callable (kernel, origin_device, dest_device,
+metadata_manager) -> PredictedKernel); the arithmetic runs in the fused device
+kernel on a batch of one.  Predictor recognises this function and batches whole
+traces instead of calling it per kernel.
+"""
+from habitat_b200.analysis.kernels import PredictedKernel
+from habitat_b200.analysis.wave_scaling import batch
+
+
+def roofline_wave_scaling(kernel, origin_device, dest_device, metadata_manager):
+    res = batch.scale_kernels([kernel], origin_device, [dest_device], metadata_manager,
+                              mode=batch.ROOFLINE)
+    batch.raise_like_reference(res.status.cpu().numpy())
+    return PredictedKernel(kernel, float(res.scaled_ns.cpu()[0, 0]))
+
+
+roofline_wave_scaling.batch_mode = batch.ROOFLINE

@@ -274,13 +274,18 @@ def segment_sum(values, offsets):
     return out
 
 
-def plane_sum(values):
+def plane_sum(values, out=None):
     """float64 sum of each row of a [P, L] float32 CUDA tensor, NaN entries skipped."""
     lib = _native.load()
     _require_cuda(values, torch.float32, "values")
     if values.ndim != 2:
         raise ValueError("values must be [planes, length]")
     P, L = values.shape
-    out = torch.empty((P,), dtype=torch.float64, device=values.device)
+    if out is None:
+        out = torch.empty((P,), dtype=torch.float64, device=values.device)
+    else:
+        _require_cuda(out, torch.float64, "out")
+        if out.numel() != P:
+            raise ValueError("out must have one entry per plane")
     _native.check(lib.hb_plane_sum(_ptr(values), L, P, _ptr(out), _native.current_stream_ptr()))
     return out
