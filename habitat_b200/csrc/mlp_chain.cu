@@ -31,9 +31,11 @@
 // bf16 (TILE_Q = 64); HB_PRECISION_BF16X3 keeps hi + lo parts of both and issues
 // the same three-product expansion for every hidden layer (TILE_Q = 32).
 //
-// Warp roles (192 threads): warp 0 = TMEM allocation + weight producer,
-// warp 1 = barrier set-up + MMA issuer, warps 2-5 = epilogue (one TMEM lane
-// quadrant each).  Every mbarrier wait is bounded: when a wait runs out the
+// Warp roles: warp 0 = TMEM allocation, warp 1 = barrier set-up + MMA issuer,
+// warps 2-5 = epilogue (one TMEM lane quadrant each), warps 6-11 = weight
+// producers.  Bulk copies issued by one thread complete one after the other
+// (measured: about 750 cycles each whatever their size), so the ring's slots
+// are dealt round-robin to several issuing warps to keep copies in flight.  Every mbarrier wait is bounded: when a wait runs out the
 // kernel records a status word, all roles leave their loops, outstanding bulk
 // copies are waited for (bounded) and TMEM is released.
 #include <cuda_bf16.h>
@@ -52,7 +54,8 @@ constexpr int kKBlk = 64;               // bf16 per 128-byte swizzle row
 constexpr int kNumMT = kWidth / kMTile; // 8
 constexpr int kNumKB = kWidth / kKBlk;  // 16
 constexpr int kTileBytes = kMTile * 128;// one weight tile image: 16 KB
-constexpr int kThreads = 192;
+constexpr int kProducerWarps = 6;        // warps 6..11; one lane of each issues bulk copies
+constexpr int kThreads = 192 + 32 * kProducerWarps;
 constexpr int kEpiThreads = 128;
 constexpr int kMaxInFeat = 12;          // F + 4 (conv2d: 8 + 4)
 
@@ -275,26 +278,29 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
 
   uint32_t issued = 0;  // producer: stage loads issued (for the drain at exit)
 
-  if (warp == 0) {
-    // ------------------------------ producer ------------------------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int t = 0; t < my_tiles && ok; ++t) {
-        const uint8_t* src = p.wpack;
-        for (int L = 0; L < n_layers && ok; ++L) {
-          const int n_loads = kNumMT * (L == 0 ? 1 : kNumKB);
-          for (int i = 0; i < n_loads; ++i, ++it) {
-            const uint32_t s = it % C::kStages;
-            const uint32_t ph = (it / C::kStages) & 1u;
-            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 0x101)) { ok = false; break; }
-            mbar_expect_tx(bar_full + 8 * s, C::kStageBytes);
-            bulk_g2s(stage0 + s * C::kStageBytes, src, C::kStageBytes, bar_full + 8 * s);
-            src += C::kStageBytes;
-          }
-        }
+  if (warp >= 6) {
+    // ------------------------------ producers -----------------------------
+    // Producer w takes loads w, w + S, w + 2S, ... (S ring slots) of the one global sequence
+    // (tile -> layer -> 128-feature block -> K block) the MMA issuer consumes.
+    // One producer per ring slot: a slot's loads are then issued in order by a
+    // single thread, which the parity protocol of its empty barrier needs.
+    static_assert(C::kStages <= kProducerWarps, "need one producer warp per ring slot");
+    if (lane == 0 && warp - 6 < C::kStages) {
+      const uint32_t w = static_cast<uint32_t>(warp - 6);
+      const uint32_t per_tile =
+          static_cast<uint32_t>(kNumMT + p.layers * kNumMT * kNumKB);
+      const uint32_t total = per_tile * static_cast<uint32_t>(my_tiles);
+      uint32_t it = w;
+      for (; it < total; it += C::kStages) {
+        const uint32_t s = it % C::kStages;
+        const uint32_t ph = (it / C::kStages) & 1u;
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 0x101)) break;
+        mbar_expect_tx(bar_full + 8 * s, C::kStageBytes);
+        bulk_g2s(stage0 + s * C::kStageBytes,
+                 p.wpack + static_cast<size_t>(it % per_tile) * C::kStageBytes, C::kStageBytes,
+                 bar_full + 8 * s);
       }
-      issued = it;
+      issued = it;  // first sequence number this producer did not issue
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------
@@ -335,7 +341,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
         }
       }
     }
-  } else {
+  } else if (warp >= 2) {
     // ------------------------------ epilogue ------------------------------
     const int e = threadIdx.x - 64;            // 0..127
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
@@ -467,18 +473,19 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
   // ------------------------------ teardown ------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) {
-    if (lane == 0 && *abort_flag) {
-      // a role gave up: wait (bounded) for bulk copies that are still landing
-      const uint32_t first = issued > static_cast<uint32_t>(C::kStages) ? issued - C::kStages : 0;
-      for (uint32_t j = first; j < issued; ++j) {
-        const uint32_t s = j % C::kStages, ph = (j / C::kStages) & 1u;
-        const long long t0 = clock64();
-        while (!mbar_try_wait(bar_full + 8 * s, ph)) {
-          if (clock64() - t0 > kWaitCycles) break;
-        }
+  if (warp >= 6 && lane == 0 && *abort_flag) {
+    // a role gave up: wait (bounded) for this producer's last copy to land
+    if (warp - 6 < C::kStages && issued >= static_cast<uint32_t>(C::kStages)) {
+      const uint32_t j = issued - C::kStages;
+      const uint32_t s = j % C::kStages, ph = (j / C::kStages) & 1u;
+      const long long t0 = clock64();
+      while (!mbar_try_wait(bar_full + 8 * s, ph)) {
+        if (clock64() - t0 > kWaitCycles) break;
       }
     }
+  }
+  __syncthreads();
+  if (warp == 0) {
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),

@@ -185,3 +185,132 @@ HB_HD int32_t hb_occupancy(const hb_dev_pre& d, int32_t block_size, int32_t smem
   occ = occ < lw ? occ : lw;
   return occ < d.blocks_limit ? occ : d.blocks_limit;
 }
+
+// ---------------------------------------------------------------------------
+// Division-free form for "ordinary" device rows (see wave_scale.cu, fast path)
+// ---------------------------------------------------------------------------
+HB_HD uint32_t hb_umulhi(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+  return __umulhi(a, b);
+#else
+  return static_cast<uint32_t>((static_cast<uint64_t>(a) * b) >> 32);
+#endif
+}
+
+constexpr int kMagicN = 512;
+
+struct FastDev {       // per destination (and origin), folded on the host
+  int32_t regs_per_block;
+  int32_t regs_units;        // (regs_per_multiprocessor / parts) >> 8
+  int32_t parts_shift;       // log2(sub-partitions)
+  int32_t gp100_units4;      // cc 6.0: (regs_per_multiprocessor / 4) >> 8, else -1
+  int32_t max_warps;
+  int32_t max_threads_per_block;
+  int32_t blocks_limit;
+  int32_t gran_shift;        // 7 or 8
+  int32_t smem_reserved;
+  int32_t smem_cap;
+  int32_t smem_pref;
+  int32_t ladder_kind;
+  int32_t smem_per_sm;
+  int32_t num_sms;
+  uint32_t sms_magic;        // for ceil(num_blocks / num_sms) in the small-kernel branch
+  float a_hi, a_lo, b_hi, b_lo;  // large branch exponent, split float64 constants
+  double log2_clk;
+};
+
+struct FastParams {
+  int32_t D;
+  int64_t K;
+  FastDev origin;
+  FastDev dest[HB_MAX_DEVICES / 2];   // the fast path takes up to 32 destinations
+};
+
+// n / d for d >= 1 with M = floor(2^32 / d) + 1 (d >= 2); exact while n * d < 2^32.
+HB_HD uint32_t udiv_magic(uint32_t n, uint32_t d, uint32_t M) {
+  return d == 1u ? n : hb_umulhi(n, M);
+}
+// Same for any n < 2^32: the estimate is the quotient or one above it.
+HB_HD uint32_t udiv_magic_fix(uint32_t n, uint32_t d, uint32_t M) {
+  if (d == 1u) return n;
+  uint32_t q = hb_umulhi(n, M);
+  if (q * d > n) --q;
+  return q;
+}
+
+struct FastKernel {   // per recorded kernel, device independent
+  int32_t block_size, wpb, regs, rpw_units, smem;
+  uint32_t m_wpb;
+};
+
+HB_HD int32_t fast_occupancy(const FastDev& d, const FastKernel& k,
+                                                  int32_t regs, int32_t rpw_units, uint32_t m_rpw,
+                                                  const uint32_t* __restrict__ s_magic) {
+  if (k.block_size <= 0 || k.block_size > d.max_threads_per_block || regs > 256 || k.smem < 0)
+    return 0;
+  // registers: allocation unit 256 per warp, checked against the per-block file
+  // with the warp count rounded up to the number of sub-partitions
+  int32_t lr = HB_INT_MAX;
+  if (rpw_units > 0) {
+    const int32_t pm = (1 << d.parts_shift) - 1;
+    const int32_t wpb_up = (k.wpb + pm) & ~pm;
+    if (d.regs_per_block < ((rpw_units * wpb_up) << 8)) return 0;
+    const uint32_t warps_part = udiv_magic(d.regs_units, rpw_units, m_rpw);
+    lr = udiv_magic(warps_part << d.parts_shift, k.wpb, k.m_wpb);
+    if (d.gp100_units4 >= 0 && lr != 0) {
+      if (d.regs_per_block < ((rpw_units * ((k.wpb + 3) & ~3)) << 8) ||
+          udiv_magic(udiv_magic(d.gp100_units4, rpw_units, m_rpw) << 2, k.wpb, k.m_wpb) == 0)
+        return 0;
+    }
+  }
+  const int32_t lw = udiv_magic(d.max_warps, k.wpb, k.m_wpb);
+  // shared memory
+  const int32_t units = (k.smem + d.smem_reserved + (1 << d.gran_shift) - 1) >> d.gran_shift;
+  const int32_t alloc = units << d.gran_shift;
+  if (alloc > d.smem_cap) return 0;
+  int32_t ls = HB_INT_MAX;
+  if (units > 0) {
+    int32_t budget = d.smem_pref;
+    if (budget < alloc) {
+      budget = d.ladder_kind == 0 ? d.smem_per_sm : hb_carveout_snap(d.ladder_kind, d.smem_per_sm, alloc);
+      if (budget < 0) return 0;
+    }
+    ls = units < kMagicN ? udiv_magic(budget >> d.gran_shift, units, s_magic[units])
+                         : (budget >> d.gran_shift) / units;
+  }
+  int32_t occ = lr < ls ? lr : ls;
+  occ = occ < lw ? occ : lw;
+  return occ < d.blocks_limit ? occ : d.blocks_limit;
+}
+
+
+// Whether a device row fits the fast path's assumptions.
+inline bool fast_row_ok(const hb_device_spec& s, const hb_dev_pre& pre) {
+  return pre.valid && s.warp_size == 32 && s.regs_per_multiprocessor <= (1 << 22) &&
+         s.regs_per_block <= (1 << 22) && s.max_threads_per_multiprocessor <= (1 << 16) &&
+         s.max_threads_per_block <= 16352 /* warps per block stay inside the magic table */ &&
+         s.shared_mem_per_multiprocessor <= (1 << 24) && s.shared_mem_per_block <= (1 << 24) &&
+         s.num_sms <= 4096 && pre.smem_reserved >= 0 && pre.smem_reserved <= (1 << 20);
+}
+
+inline uint32_t magic_of(uint32_t d) { return d >= 2 ? static_cast<uint32_t>((1ull << 32) / d) + 1u : 0u; }
+
+inline FastDev fold_fast(const hb_device_spec& s, const hb_dev_pre& pre) {
+  FastDev f{};
+  f.regs_per_block = pre.regs_per_block;
+  f.regs_units = pre.regs_per_part >> 8;
+  f.parts_shift = pre.parts == 2 ? 1 : 2;
+  f.gp100_units4 = pre.gp100 ? (pre.regs_per_part4 >> 8) : -1;
+  f.max_warps = pre.max_warps;
+  f.max_threads_per_block = pre.max_threads_per_block;
+  f.blocks_limit = pre.blocks_limit;
+  f.gran_shift = pre.smem_gran == 128 ? 7 : 8;
+  f.smem_reserved = pre.smem_reserved;
+  f.smem_cap = pre.smem_cap;
+  f.smem_pref = pre.smem_pref;
+  f.ladder_kind = pre.ladder_kind;
+  f.smem_per_sm = pre.smem_per_sm;
+  f.num_sms = s.num_sms;
+  f.sms_magic = magic_of(static_cast<uint32_t>(s.num_sms));
+  return f;
+}

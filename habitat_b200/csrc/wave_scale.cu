@@ -211,24 +211,192 @@ wave_scale_kernel(const Ptrs p, const __grid_constant__ LaunchParams lp) {
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Fast path.  The generic kernel above spends its time in the transcendental /
+// conversion unit: every integer division compiles to reciprocal + conversion
+// sequences, about ninety such operations per pair, and that unit issues sixteen
+// lanes per clock.  When every row of the launch is "ordinary" (valid, warp size
+// 32, fields small enough for 32-bit magic numbers - true of every real GPU) the
+// divisions become multiply-high by magic numbers M[d] = floor(2^32 / d) + 1
+// looked up in shared memory:
+//   * divisors that depend on the kernel only (warps per block, register
+//     allocation units, shared-memory allocation units) index one 512-entry
+//     table loaded from global memory;
+//   * the wave size of a pair is num_sms * occupancy with occupancy <= 32, so
+//     each device gets a 33-entry table built at block start.
+// ---------------------------------------------------------------------------
+__device__ uint32_t g_magic[kMagicN];   // filled by hb_set_devices
+
+template <int VEC, bool DEST_REGS>
+__global__ void __launch_bounds__(256)
+wave_scale_fast_kernel(const Ptrs p, const __grid_constant__ FastParams fp) {
+  __shared__ uint32_t s_magic[kMagicN];
+  __shared__ uint32_t s_wave_magic[HB_MAX_DEVICES / 2 + 1][33];
+  __shared__ double s_log2[33];
+  for (int i = threadIdx.x; i < kMagicN; i += blockDim.x) s_magic[i] = g_magic[i];
+  for (int i = threadIdx.x; i < (fp.D + 1) * 33; i += blockDim.x) {
+    const int d = i / 33, occ = i - d * 33;
+    const uint32_t wave = static_cast<uint32_t>((d == 0 ? fp.origin.num_sms : fp.dest[d - 1].num_sms) * occ);
+    s_wave_magic[d][occ] = wave >= 2u ? 0xFFFFFFFFu / wave + ((0xFFFFFFFFu % wave) + 1u == wave ? 1u : 0u) + 1u : 0u;
+  }
+  if (threadIdx.x < 33) s_log2[threadIdx.x] = c_log2_int[threadIdx.x];
+  __syncthreads();
+
+  const int64_t K = fp.K;
+  const int64_t k0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
+  if (k0 >= K) return;
+
+  const Vec<int32_t, VEC> nbv = load_vec<int32_t, VEC>(p.num_blocks + k0);
+  const Vec<uint16_t, VEC> bsv = load_vec<uint16_t, VEC>(p.block_size + k0);
+  const Vec<uint16_t, VEC> rgv = load_vec<uint16_t, VEC>(p.regs + k0);
+  const Vec<uint32_t, VEC> smv = load_vec<uint32_t, VEC>(p.smem + k0);
+  const Vec<float, VEC> tv = load_vec<float, VEC>(p.time_ns + k0);
+  const Vec<float, VEC> gv = load_vec<float, VEC>(p.gamma + k0);
+
+  FastKernel fk[VEC];
+  uint32_t m_rpw[VEC];
+  int32_t wave_o[VEC], omax[VEC];
+  Vec<uint8_t, VEC> oocc;
+  Vec<uint32_t, VEC> owav;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    FastKernel& k = fk[i];
+    k.block_size = bsv.v[i];
+    k.wpb = (k.block_size + 31) >> 5;
+    k.regs = rgv.v[i];
+    k.rpw_units = (k.regs + 7) >> 3;               // roundup(regs * 32, 256) / 256
+    k.smem = smv.v[i] > 0x7FFF0000u ? -1 : static_cast<int32_t>(smv.v[i]);
+    k.m_wpb = s_magic[min(k.wpb, kMagicN - 1)];    // wpb <= 32 whenever the block can run
+    m_rpw[i] = s_magic[min(k.rpw_units, kMagicN - 1)];
+    const int32_t occ = fast_occupancy(fp.origin, k, k.regs, k.rpw_units, m_rpw[i], s_magic);
+    const int32_t nb = nbv.v[i];
+    wave_o[i] = fp.origin.num_sms * occ;
+    oocc.v[i] = static_cast<uint8_t>(occ);
+    owav.v[i] = (occ > 0 && nb >= 1)
+                    ? udiv_magic_fix(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_o[i]),
+                                     s_wave_magic[0][occ])
+                    : 0xFFFFFFFFu;
+    omax[i] = (nb >= 1 && nb < wave_o[i])
+                  ? static_cast<int32_t>(udiv_magic(nb + fp.origin.num_sms - 1, fp.origin.num_sms,
+                                                    fp.origin.sms_magic))
+                  : 1;
+  }
+  store_vec<uint8_t, VEC>(p.origin_occ + k0, oocc);
+  store_vec<uint32_t, VEC>(p.origin_waves + k0, owav);
+
+  for (int d = 0; d < fp.D; ++d) {
+    const FastDev& dd = fp.dest[d];
+    const int64_t base = static_cast<int64_t>(d) * K + k0;
+    Vec<float, VEC> outv;
+    Vec<uint8_t, VEC> occv;
+    Vec<uint32_t, VEC> wavv;
+    Vec<int16_t, VEC> drv;
+    if (DEST_REGS) drv = load_vec<int16_t, VEC>(p.dest_regs + base);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int32_t nb = nbv.v[i];
+      int32_t regs = fk[i].regs, units = fk[i].rpw_units;
+      uint32_t m = m_rpw[i];
+      if (DEST_REGS && drv.v[i] >= 0) {
+        regs = drv.v[i];
+        units = (regs + 7) >> 3;
+        m = s_magic[min(units, kMagicN - 1)];
+      }
+      const int32_t occ = fast_occupancy(dd, fk[i], regs, units, m, s_magic);
+      const int32_t wave_d = dd.num_sms * occ;
+      occv.v[i] = static_cast<uint8_t>(occ);
+      wavv.v[i] = (occ > 0 && nb >= 1)
+                      ? udiv_magic_fix(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_d),
+                                       s_wave_magic[d + 1][occ])
+                      : 0xFFFFFFFFu;
+      const float gamma = gv.v[i];
+      float e;
+      bool ok = nb >= 1 && wave_o[i] != 0;
+      if (ok && nb < wave_o[i] && nb < wave_d) {
+        // small kernel (roofline.py:32-45); both per-SM block counts are <= 32
+        const int32_t dmax = static_cast<int32_t>(udiv_magic(nb + dd.num_sms - 1, dd.num_sms, dd.sms_magic));
+        e = static_cast<float>((1.0 - static_cast<double>(gamma)) *
+                               (dd.log2_clk + s_log2[dmax] - s_log2[omax[i]]));
+      } else {
+        ok = ok && !(nb < wave_o[i] && wave_d == 0);
+        e = fmaf(gamma, dd.a_hi, dd.b_hi) + fmaf(gamma, dd.a_lo, dd.b_lo);
+      }
+      outv.v[i] = ok ? tv.v[i] * exp2f(e) : __int_as_float(0x7FC00000);
+    }
+    store_vec<float, VEC>(p.scaled_ns + base, outv);
+    store_vec<uint8_t, VEC>(p.dest_occ + base, occv);
+    store_vec<uint32_t, VEC>(p.dest_waves + base, wavv);
+  }
+}
+
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool vec4_ok(const Ptrs& p, int64_t K, bool need_gamma) {
+  // The 4-wide path needs every plane base (d * K elements in) and every input
+  // to sit on a 16-byte boundary for its widest type.
+  return (K % 4 == 0) && aligned16(p.num_blocks) && aligned16(p.smem) && aligned16(p.time_ns) &&
+         (!need_gamma || aligned16(p.gamma)) && aligned16(p.scaled_ns) && aligned16(p.dest_waves) &&
+         aligned16(p.origin_waves) && (reinterpret_cast<uintptr_t>(p.block_size) % 8 == 0) &&
+         (reinterpret_cast<uintptr_t>(p.regs) % 8 == 0) &&
+         (reinterpret_cast<uintptr_t>(p.dest_occ) % 4 == 0) &&
+         (reinterpret_cast<uintptr_t>(p.origin_occ) % 4 == 0) &&
+         (!p.status || reinterpret_cast<uintptr_t>(p.status) % 4 == 0) &&
+         (!p.dest_regs || reinterpret_cast<uintptr_t>(p.dest_regs) % 8 == 0);
+}
+
+// Fast path when every row of the launch qualifies and only the five standard
+// outputs are wanted; returns false (nothing launched) otherwise.
+bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream, hb_status* st) {
+  if (p.status || p.limits || lp.D > HB_MAX_DEVICES / 2) return false;
+  if (!fast_row_ok(g_rows[lp.origin_row], g_pre[lp.origin_row])) return false;
+  for (int d = 0; d < lp.D; ++d)
+    if (!fast_row_ok(g_rows[lp.dest_row[d]], g_pre[lp.dest_row[d]])) return false;
+  FastParams fp{};
+  fp.D = lp.D;
+  fp.K = lp.K;
+  fp.origin = fold_fast(g_rows[lp.origin_row], g_pre[lp.origin_row]);
+  for (int d = 0; d < lp.D; ++d) {
+    FastDev& f = fp.dest[d];
+    f = fold_fast(g_rows[lp.dest_row[d]], g_pre[lp.dest_row[d]]);
+    f.a_hi = static_cast<float>(lp.a[d]);
+    f.a_lo = static_cast<float>(lp.a[d] - static_cast<double>(f.a_hi));
+    f.b_hi = static_cast<float>(lp.b[d]);
+    f.b_lo = static_cast<float>(lp.b[d] - static_cast<double>(f.b_hi));
+    f.log2_clk = lp.log2_clk[d];
+  }
+  const int64_t K = lp.K;
+  const bool vec4 = vec4_ok(p, K, true);
+  const int threads = 256, vec = vec4 ? 4 : 1;
+  const int64_t blocks = ((K + vec - 1) / vec + threads - 1) / threads;
+  if (blocks > 0x7FFFFFFF) {
+    hb::set_error("hb_wave_scale: K too large for one launch");
+    *st = HB_ERR_TOO_LARGE;
+    return true;
+  }
+  const dim3 grid(static_cast<unsigned>(blocks));
+  if (vec4) {
+    if (p.dest_regs) wave_scale_fast_kernel<4, true><<<grid, threads, 0, stream>>>(p, fp);
+    else wave_scale_fast_kernel<4, false><<<grid, threads, 0, stream>>>(p, fp);
+  } else {
+    if (p.dest_regs) wave_scale_fast_kernel<1, true><<<grid, threads, 0, stream>>>(p, fp);
+    else wave_scale_fast_kernel<1, false><<<grid, threads, 0, stream>>>(p, fp);
+  }
+  const cudaError_t e = cudaGetLastError();
+  *st = e == cudaSuccess ? HB_OK : hb::cuda_fail(e, "wave_scale_fast_kernel launch");
+  return true;
+}
 
 template <bool METRICS>
 hb_status launch(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream) {
   const int64_t K = lp.K;
   const bool extra = p.status != nullptr || p.limits != nullptr;
-  // The 4-wide path needs every plane base (d * K elements in) and every input
-  // to sit on a 16-byte boundary for its widest type.
-  const bool vec4 = (K % 4 == 0) && aligned16(p.num_blocks) && aligned16(p.smem) &&
-                    aligned16(p.time_ns) && (METRICS || aligned16(p.gamma)) &&
-                    aligned16(p.scaled_ns) && aligned16(p.dest_waves) &&
-                    aligned16(p.origin_waves) &&
-                    (reinterpret_cast<uintptr_t>(p.block_size) % 8 == 0) &&
-                    (reinterpret_cast<uintptr_t>(p.regs) % 8 == 0) &&
-                    (reinterpret_cast<uintptr_t>(p.dest_occ) % 4 == 0) &&
-                    (reinterpret_cast<uintptr_t>(p.origin_occ) % 4 == 0) &&
-                    (!p.status || reinterpret_cast<uintptr_t>(p.status) % 4 == 0) &&
-                    (!p.dest_regs || reinterpret_cast<uintptr_t>(p.dest_regs) % 8 == 0);
+  if (!METRICS) {
+    hb_status fast_st = HB_OK;
+    if (try_launch_fast(p, lp, stream, &fast_st)) return fast_st;
+  }
+  const bool vec4 = vec4_ok(p, K, !METRICS);
   const int threads = 256;
   const int vec = vec4 ? 4 : 1;
   const int64_t nthreads = (K + vec - 1) / vec;
@@ -345,6 +513,9 @@ extern "C" hb_status hb_set_devices(const hb_device_spec* rows, int32_t n) {
   lg[0] = 0.0;
   for (int i = 1; i <= 64; ++i) lg[i] = std::log2(static_cast<double>(i));
   HB_CUDA_TRY(cudaMemcpyToSymbol(c_log2_int, lg, sizeof(lg)));
+  uint32_t magic[kMagicN];
+  for (int i = 0; i < kMagicN; ++i) magic[i] = magic_of(static_cast<uint32_t>(i));
+  HB_CUDA_TRY(cudaMemcpyToSymbol(g_magic, magic, sizeof(magic)));
   return HB_OK;
 }
 

@@ -90,3 +90,27 @@ def wave_scale_batch(spec_tuples, origin_row, dest_rows, kernels, dest_regs=None
         p(out["scaled_ns"]), p(out["dest_occupancy"]), p(out["dest_waves"]),
         p(out["origin_occupancy"]), p(out["origin_waves"]), p(out["status"]), p(out["limits"]))
     return out
+
+
+def wave_scale_pair(origin_spec, dest_spec, num_blocks, block_size, smem_total, regs, dest_regs,
+                    run_time_ns, gamma):
+    """One pair with a float64 gamma: returns (status, scaled_ns, origin_occ, dest_occ)."""
+    L = lib()
+    if not getattr(L, "_pair_ready", False):
+        L.hbo_wave_scale_pair.restype = ctypes.c_int
+        L.hbo_wave_scale_pair.argtypes = [
+            ctypes.POINTER(Device), ctypes.POINTER(Device), ctypes.c_int32, ctypes.c_int,
+            ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_double,
+            ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+            ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
+        L._pair_ready = True
+    o = Device(*[int(v) for v in origin_spec])
+    d = Device(*[int(v) for v in dest_spec])
+    out = ctypes.c_double()
+    oo, od = ctypes.c_int(), ctypes.c_int()
+    wo, wd = ctypes.c_int64(), ctypes.c_int64()
+    st = L.hbo_wave_scale_pair(ctypes.byref(o), ctypes.byref(d), int(num_blocks), int(block_size),
+                               int(smem_total), int(regs), int(dest_regs), float(run_time_ns),
+                               float(gamma), ctypes.byref(out), ctypes.byref(oo), ctypes.byref(od),
+                               ctypes.byref(wo), ctypes.byref(wd))
+    return st, out.value, oo.value, od.value

@@ -29,9 +29,16 @@ def run_wave_gpu(kernels, origin, dests, dest_regs=None, metrics=None):
     res = batched.wave_scale(kb, origin, dests, dest_regs=dr, metrics=mb, want_status=True,
                              want_limits=True)
     torch.cuda.synchronize()
-    return {k: to_numpy(getattr(res, k)) for k in
-            ("scaled_ns", "dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves",
-             "status", "limits")}
+    out = {k: to_numpy(getattr(res, k)) for k in
+           ("scaled_ns", "dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves",
+            "status", "limits")}
+    if metrics is None:
+        # the same call without the verification outputs takes the division-free kernel
+        fast = batched.wave_scale(kb, origin, dests, dest_regs=dr)
+        torch.cuda.synchronize()
+        out["fast"] = {k: to_numpy(getattr(fast, k)) for k in
+                       ("scaled_ns", "dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves")}
+    return out
 
 
 def run_wave_oracle(kernels, origin, dests, dest_regs=None):
@@ -45,12 +52,17 @@ def assert_wave_equal(got, ref, rel=1e-6):
     for key in ("dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves", "status", "limits"):
         assert np.array_equal(got[key], ref[key]), key
     ok = ref["status"] <= 1
-    assert np.isnan(got["scaled_ns"][~ok]).all()
-    g = got["scaled_ns"][ok].astype(np.float64)
-    r = ref["scaled_ns"][ok]
-    assert np.isfinite(g).all()
-    if g.size:
-        err = np.abs(g - r) / np.abs(r)
-        assert err.max() <= rel, err.max()
-        return float(err.max())
-    return 0.0
+    worst = 0.0
+    variants = [got] + ([got["fast"]] if "fast" in got else [])
+    for v in variants:
+        for key in ("dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves"):
+            assert np.array_equal(v[key], ref[key]), key
+        assert np.isnan(v["scaled_ns"][~ok]).all()
+        g = v["scaled_ns"][ok].astype(np.float64)
+        r = ref["scaled_ns"][ok]
+        assert np.isfinite(g).all()
+        if g.size:
+            err = np.abs(g - r) / np.abs(r)
+            assert err.max() <= rel, err.max()
+            worst = max(worst, float(err.max()))
+    return worst

@@ -21,7 +21,9 @@ def harness(tmp_path_factory):
                     os.path.join(HERE, "occupancy_host_harness.cpp"), "-o", out], check=True)
     lib = ctypes.CDLL(out)
     lib.harness_occupancy.restype = None
-    return lib.harness_occupancy
+    lib.harness_fast_occupancy.restype = None
+    lib.harness_magic_errors.restype = ctypes.c_long
+    return lib
 
 
 def _run(harness, spec, block, smem, regs):
@@ -30,7 +32,12 @@ def _run(harness, spec, block, smem, regs):
     occ = np.empty(n, np.int32)
     lim = np.empty((n, 4), np.int32)
     p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
-    harness(ctypes.byref(d), ctypes.c_long(n), p(block), p(smem), p(regs), p(occ), p(lim))
+    harness.harness_occupancy(ctypes.byref(d), ctypes.c_long(n), p(block), p(smem), p(regs), p(occ), p(lim))
+    fast = np.empty(n, np.int32)
+    harness.harness_fast_occupancy(ctypes.byref(d), ctypes.c_long(n), p(block), p(smem), p(regs), p(fast))
+    if (fast >= 0).any():
+        # the division-free form must agree wherever the row qualifies for it
+        assert np.array_equal(fast, occ), "fast path disagrees"
     return occ, lim
 
 
@@ -74,3 +81,20 @@ def test_odd_device_rows(harness):
         for i in range(n):
             o, l = owave.occupancy(spec, block[i], smem[i], regs[i])
             assert occ[i] == o and list(lim[i]) == l, (v, block[i], smem[i], regs[i])
+
+
+def test_magic_division(harness):
+    assert harness.harness_magic_errors() == 0
+
+
+def test_fast_path_covers_shipped_rows(harness, device_file):
+    g = np.random.Generator(np.random.PCG64(8))
+    block = g.integers(1, 1100, 100).astype(np.int32)
+    regs = g.integers(0, 300, 100).astype(np.int32)
+    smem = g.integers(0, 100000, 100).astype(np.int32)
+    for name, dev in device_file.items():
+        d = _native.DeviceSpec(*[int(v) for v in dev.spec_tuple()])
+        fast = np.empty(100, np.int32)
+        p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        harness.harness_fast_occupancy(ctypes.byref(d), ctypes.c_long(100), p(block), p(smem), p(regs), p(fast))
+        assert (fast >= 0).all(), name
