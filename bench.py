@@ -411,7 +411,7 @@ def main():
                                        "GPU and step, bf16 tensor cores, fp32 accumulate",
                            "l2": "weights (16.5 MB of bf16 tiles) stay in L2 by design; the kernel is "
                                  "tensor-bound, per-query HBM traffic is 37 B"},
-                "roofline": {"bound": "tensor", "kernel": "mlp_chain_kernel<64,false>", "achieved": tflops,
+                "roofline": {"bound": "tensor", "kernel": "mlp_chain_pair_kernel", "achieved": tflops,
                              "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                              "frac": tflops / peaks["bf16_tflops"],
                              "frac_of_sustained": tflops / peaks["bf16_tflops_sustained"],

@@ -495,6 +495,409 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
 }
 
 // ---------------------------------------------------------------------------
+// Two-CTA form (bf16 mode).  A single CTA can only keep 64 queries on chip,
+// and an M = 128 MMA with N = 64 occupies the tensor core for the same 64 cycles
+// as one with N = 128, so the one-CTA kernel tops out at half rate.  Here two
+// CTAs of a cluster share one tile of 128 queries:
+//   * tcgen05.mma.cta_group::2 with M = 256, N = 128: CTA c supplies the A rows
+//     (weights) of features 256 j + 128 c .. and the B rows (activations) of
+//     queries 64 c .. 64 c + 63; its TMEM receives the D rows of its features
+//     for all 128 queries.  Each weight byte is fetched once per pair.
+//   * The leader CTA (rank 0) issues every MMA.  A ring slot is ready when the
+//     leader's own bulk copy and the peer's have landed; the peer relays the
+//     completion of its copy with a remote mbarrier arrive.  tcgen05.commit
+//     multicasts "slot free" and "layer done" to both CTAs.
+//   * The epilogue of CTA c holds features x all 128 queries, but the next
+//     layer needs, in each CTA, all features x its 64 queries: half of the
+//     bf16 results are stored into the peer's shared memory (st.shared::cluster).
+//   * fc2: each CTA reduces its 512 features to 128 partial sums, hands the 64
+//     that belong to the peer's queries over through the peer's shared memory,
+//     and finishes its own 64 queries.
+// ---------------------------------------------------------------------------
+constexpr int kPairQ = 128;                 // queries per cluster tile
+constexpr int kPairHalfQ = 64;              // activation rows resident per CTA
+constexpr int kPairMT = kWidth / 256;       // 4 MMA row blocks per layer
+constexpr int kPairStages = 6;
+constexpr int kPairActKb = kPairHalfQ * 128;          // 8 KB per K block
+constexpr int kPairActBytes = kNumKB * kPairActKb;    // 128 KB
+constexpr int kPairSmemBytes = kPairActBytes + kPairStages * kTileBytes + 1024 + 1024;
+static_assert(kPairSmemBytes <= 232448, "over the 227 KB shared-memory limit");
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag, int32_t* status,
+                                                  int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void st_cluster_b16(uint32_t cluster_addr, __nv_bfloat16 v) {
+  asm volatile("st.shared::cluster.b16 [%0], %1;" ::"r"(cluster_addr),
+               "h"(__bfloat16_as_ushort(v))
+               : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
+                   : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(bar),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+
+  const uint32_t act = base;
+  const uint32_t stage0 = base + kPairActBytes;
+  const uint32_t bars = stage0 + kPairStages * kTileBytes;
+  uint8_t* bars_ptr = base_ptr + (bars - base);
+  // barrier block (same offsets in both CTAs)
+  const uint32_t bar_full = bars;                          // [stages] own bulk copy landed
+  const uint32_t bar_peer_full = bars + 8 * kPairStages;   // [stages] leader only: peer's copy landed
+  const uint32_t bar_empty = bars + 16 * kPairStages;      // [stages] slot consumed (multicast commit)
+  const uint32_t bar_acc = bars + 24 * kPairStages;        // layer accumulated (multicast commit)
+  const uint32_t bar_act = bar_acc + 8;                    // leader only: both epilogues done
+  const uint32_t bar_fc2 = bar_acc + 16;                   // peer's fc2 partial sums arrived
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 24 * kPairStages + 24);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 24 * kPairStages + 28);
+  volatile int* epi_ok = reinterpret_cast<volatile int*>(bars_ptr + 24 * kPairStages + 32);
+  float* fc2_mine = reinterpret_cast<float*>(bars_ptr + 512);    // [64] own queries, own features
+  float* fc2_peer = reinterpret_cast<float*>(bars_ptr + 768);    // [64] own queries, peer's features
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t peer = rank ^ 1u;
+
+  if (threadIdx.x == 32) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_peer_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    mbar_init(bar_act, 2);
+    mbar_init(bar_fc2, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_layers = p.layers + 1;
+  const int n_pairs = static_cast<int>(gridDim.x >> 1);
+  const int pair_id = static_cast<int>(blockIdx.x >> 1);
+  int my_tiles = 0;
+  if (pair_id < p.num_tiles) my_tiles = (p.num_tiles - 1 - pair_id) / n_pairs + 1;
+  const uint32_t loads_per_tile = static_cast<uint32_t>(kPairMT + p.layers * kPairMT * kNumKB);
+
+  uint32_t issued = 0;
+
+  if (warp >= 6) {
+    // ------------------------------ producers -----------------------------
+    // One producer per ring slot.  The pack is laid out per 128-feature block
+    // (layer -> block -> K block); this CTA streams blocks 2 j + rank.
+    if (lane == 0 && warp - 6 < kPairStages) {
+      const uint32_t w = static_cast<uint32_t>(warp - 6);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        size_t layer_base = 0;   // in tile images
+        for (int L = 0; L < n_layers && ok; ++L) {
+          const int nkb = L == 0 ? 1 : kNumKB;
+          for (int j = 0; j < kPairMT && ok; ++j) {
+            const size_t blk = layer_base + static_cast<size_t>(2 * j + rank) * nkb;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+              if (it % kPairStages != w) continue;
+              const uint32_t ph = (it / kPairStages) & 1u;
+              if (!mbar_wait(bar_empty + 8 * w, ph ^ 1u, abort_flag, p.status, 0x111)) { ok = false; break; }
+              mbar_expect_tx(bar_full + 8 * w, kTileBytes);
+              bulk_g2s(stage0 + w * kTileBytes, p.wpack + (blk + kb) * kTileBytes, kTileBytes,
+                       bar_full + 8 * w);
+              issued = it + 1;
+            }
+          }
+          layer_base += static_cast<size_t>(kNumMT) * nkb;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ------------------------------ MMA issuer (leader) -------------------
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                 (static_cast<uint32_t>(kPairQ >> 3) << 17) |
+                                 (static_cast<uint32_t>(256 >> 4) << 24);
+      const uint64_t desc_hi = (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) |
+                               (static_cast<uint64_t>(2) << 61) | (static_cast<uint64_t>(1) << 16);
+      const uint32_t a_lo0 = (stage0 & 0x3FFFF) >> 4;
+      const uint32_t b_lo0 = (act & 0x3FFFF) >> 4;
+      uint32_t s = 0, ph = 0, lay = 0;
+      bool ok = true;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        for (int L = 0; L < n_layers && ok; ++L, ++lay) {
+          if (!mbar_wait_cluster(bar_act, lay & 1u, abort_flag, p.status, 0x211)) { ok = false; break; }
+          tc_fence_after();
+          const int nkb = L == 0 ? 1 : kNumKB;
+          for (int j = 0; j < kPairMT && ok; ++j) {
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(j * kPairQ);
+            for (int kb = 0; kb < nkb; ++kb) {
+              if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x212) ||
+                  !mbar_wait_cluster(bar_peer_full + 8 * s, ph, abort_flag, p.status, 0x213)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              const uint64_t a0 = desc_hi | (a_lo0 + s * (kTileBytes >> 4));
+              const uint64_t b0 = desc_hi | (b_lo0 + static_cast<uint32_t>(kb) * (kPairActKb >> 4));
+              tc_mma_pair_bf16(d_tmem, a0, b0, idesc, kb != 0 ? 1u : 0u);
+              tc_mma_pair_bf16(d_tmem, a0 + 2, b0 + 2, idesc, 1u);
+              tc_mma_pair_bf16(d_tmem, a0 + 4, b0 + 4, idesc, 1u);
+              tc_mma_pair_bf16(d_tmem, a0 + 6, b0 + 6, idesc, 1u);
+              tc_commit_pair(bar_empty + 8 * s);
+              if (++s == kPairStages) { s = 0; ph ^= 1u; }
+            }
+          }
+          if (ok) tc_commit_pair(bar_acc);
+        }
+      }
+    } else if (lane == 0 && rank == 1) {
+      // ------------------------------ relay (peer) --------------------------
+      // Tells the leader that this CTA's half of a ring slot has landed.
+      const uint32_t total = loads_per_tile * static_cast<uint32_t>(my_tiles);
+      uint32_t s = 0, ph = 0;
+      for (uint32_t it = 0; it < total; ++it) {
+        if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x411)) break;
+        mbar_arrive_remote(map_to_cta(bar_peer_full + 8 * s, 0));
+        if (++s == kPairStages) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else if (warp >= 2) {
+    // ------------------------------ epilogue ------------------------------
+    const int e = threadIdx.x - 64;            // 0..127
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;            // feature row inside this CTA's 128-row block
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const int C_in = p.n_op_feat + 4;
+    const uint32_t act_peer = map_to_cta(act, peer);
+    const uint32_t bar_act_leader = map_to_cta(bar_act, 0);
+    uint32_t lay = 0, tile_no = 0;
+    bool ok = true;
+    float* red = reinterpret_cast<float*>(base_ptr);   // [128][65], aliases activations
+
+    for (int t = 0; t < my_tiles && ok; ++t, ++tile_no) {
+      const int tile = pair_id + t * n_pairs;
+      const int64_t q0 = static_cast<int64_t>(tile) * kPairQ + static_cast<int64_t>(rank) * kPairHalfQ;
+
+      if (e < kPairHalfQ) {
+        const int64_t q = q0 + e;
+        __nv_bfloat16 row[kKBlk];
+#pragma unroll
+        for (int c = 0; c < kKBlk; ++c) row[c] = __float2bfloat16_rn(0.0f);
+        if (q < p.Q) {
+          int dr = p.dev_row[q];
+          dr = dr < p.n_dev ? dr : p.n_dev - 1;
+          for (int c = 0; c < C_in; ++c) {
+            const double x = c < p.n_op_feat
+                                 ? static_cast<double>(p.feats[q * p.n_op_feat + c])
+                                 : p.dev_feat[dr * 4 + (c - p.n_op_feat)];
+            const float xn = static_cast<float>((x - p.mu[c]) / p.sigma[c]);
+            const __nv_bfloat16 hi = __float2bfloat16_rn(xn);
+            const __nv_bfloat16 lo = __float2bfloat16_rn(xn - __bfloat162float(hi));
+            row[c] = hi;
+            row[C_in + c] = lo;
+            row[2 * C_in + c] = hi;
+          }
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(row);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint4* dst = reinterpret_cast<uint4*>(base_ptr + e * 128 + (((ch ^ e) & 7) << 4));
+          *dst = src[ch];
+        }
+      }
+      fence_proxy_async();
+      epi_bar_sync();
+      if (e == 0) {
+        if (rank == 0) mbar_arrive(bar_act);
+        else mbar_arrive_remote(bar_act_leader);
+      }
+
+      for (int L = 0; L < n_layers && ok; ++L, ++lay) {
+        if (e == 0) *epi_ok = mbar_wait(bar_acc, lay & 1u, abort_flag, p.status, 0x311) ? 1 : 0;
+        epi_bar_sync();
+        if (*epi_ok == 0) { ok = false; break; }
+        tc_fence_after();
+        const float* bias = p.bias + L * kWidth;
+        const bool last = (L == n_layers - 1);
+        if (!last) {
+#pragma unroll 1
+          for (int j = 0; j < kPairMT; ++j) {
+            const int f = j * 256 + static_cast<int>(rank) * 128 + r;   // feature = next layer's K index
+            const float b = __ldg(bias + f);
+            const uint32_t kb_off = static_cast<uint32_t>(f >> 6) * kPairActKb;
+            const uint32_t col = static_cast<uint32_t>(f & 63);
+#pragma unroll
+            for (int h = 0; h < kPairQ / 32; ++h) {
+              float v[32];
+              tc_ld32(t_lane + static_cast<uint32_t>(j * kPairQ + h * 32), v);
+              const bool mine = static_cast<uint32_t>(h >> 1) == rank;   // queries 64 (h / 2) ..
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const uint32_t n = static_cast<uint32_t>((h & 1) * 32 + i);   // row in the owner's buffer
+                const __nv_bfloat16 hi = __float2bfloat16_rn(fmaxf(v[i] + b, 0.0f));
+                const uint32_t off = kb_off + swz_off(n, col);
+                if (mine) *reinterpret_cast<__nv_bfloat16*>(base_ptr + off) = hi;
+                else st_cluster_b16(act_peer + off, hi);
+              }
+            }
+          }
+          tc_fence_before();
+          asm volatile("fence.proxy.async;" ::: "memory");   // local and peer shared memory
+          epi_bar_sync();
+          if (e == 0) {
+            if (rank == 0) mbar_arrive(bar_act);
+            else mbar_arrive_remote(bar_act_leader);
+          }
+        } else {
+          // fc2 over this CTA's 512 features, 64 queries at a time
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            float acc[kPairHalfQ];
+#pragma unroll
+            for (int i = 0; i < kPairHalfQ; ++i) acc[i] = 0.0f;
+#pragma unroll 1
+            for (int j = 0; j < kPairMT; ++j) {
+              const int f = j * 256 + static_cast<int>(rank) * 128 + r;
+              const float b = __ldg(bias + f);
+              const float w = __ldg(p.fc2_w + f);
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                float v[32];
+                tc_ld32(t_lane + static_cast<uint32_t>(j * kPairQ + half * 64 + h * 32), v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  acc[h * 32 + i] = fmaf(w, fmaxf(v[i] + b, 0.0f), acc[h * 32 + i]);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < kPairHalfQ; ++i) red[r * (kPairHalfQ + 1) + i] = acc[i];
+            epi_bar_sync();
+            const int n = e & 63, part = e >> 6;
+            float s = 0.0f;
+            for (int k = 0; k < 64; ++k) s += red[(part * 64 + k) * (kPairHalfQ + 1) + n];
+            epi_bar_sync();
+            red[part * 64 + n] = s;
+            epi_bar_sync();
+            if (e < kPairHalfQ) {
+              const float tot = red[e] + red[64 + e];
+              if (static_cast<uint32_t>(half) == rank) fc2_mine[e] = tot;
+              else st_cluster_f32(map_to_cta(smem_u32(fc2_peer + e), peer), tot);
+            }
+            epi_bar_sync();
+          }
+          tc_fence_before();
+          // hand-over of the partial sums, then the owner finishes its 64 queries
+          if (e == 0) {
+            mbar_arrive_remote(map_to_cta(bar_fc2, peer));
+            *epi_ok = mbar_wait_cluster(bar_fc2, tile_no & 1u, abort_flag, p.status, 0x312) ? 1 : 0;
+          }
+          epi_bar_sync();
+          if (*epi_ok == 0) { ok = false; break; }
+          if (e < kPairHalfQ) {
+            const int64_t q = q0 + e;
+            if (q < p.Q) p.out[q] = fc2_mine[e] + fc2_peer[e] + p.fc2_b;
+          }
+          epi_bar_sync();
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp >= 6 && lane == 0 && *abort_flag && warp - 6 < kPairStages && issued > 0) {
+    const uint32_t j = issued - 1;
+    const uint32_t ph = (j / kPairStages) & 1u;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar_full + 8 * (warp - 6), ph)) {
+      if (clock64() - t0 > kWaitCycles) break;
+    }
+  }
+  __syncthreads();
+  cluster_sync_all();   // neither CTA leaves while the other may still touch its memory
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Host side: weight packing and launch
 // ---------------------------------------------------------------------------
 uint16_t f32_to_bf16(float f) {
@@ -622,8 +1025,8 @@ extern "C" hb_status hb_mlp_create(hb_mlp** handle, int32_t n_op_features, int32
   if ((e = cudaMalloc(reinterpret_cast<void**>(&h->status), sizeof(int32_t))) != cudaSuccess)
     return fail(e, "cudaMalloc status");
   if ((e = cudaMemset(h->status, 0, sizeof(int32_t))) != cudaSuccess) return fail(e, "cudaMemset");
-  e = cudaFuncSetAttribute(mlp_chain_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           Cfg<64, false>::kSmemBytes);
+  e = cudaFuncSetAttribute(mlp_chain_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kPairSmemBytes);
   if (e != cudaSuccess) return fail(e, "cudaFuncSetAttribute");
   e = cudaFuncSetAttribute(mlp_chain_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            Cfg<32, true>::kSmemBytes);
@@ -640,7 +1043,7 @@ extern "C" hb_status hb_mlp_predict(hb_mlp* h, const float* op_features, const u
   }
   if (Q == 0) return HB_OK;
   const bool split = h->precision == HB_PRECISION_BF16X3;
-  const int tile_q = split ? 32 : 64;
+  const int tile_q = split ? 32 : kPairQ;
   const int64_t tiles = (Q + tile_q - 1) / tile_q;
   if (tiles > 0x7FFFFFFF) {
     hb::set_error("hb_mlp_predict: Q too large for one launch");
@@ -652,10 +1055,15 @@ extern "C" hb_status hb_mlp_predict(hb_mlp* h, const float* op_features, const u
   p.n_op_feat = h->n_op_feat; p.layers = h->layers; p.feats = op_features;
   p.dev_row = device_row; p.Q = Q; p.out = out; p.num_tiles = static_cast<int32_t>(tiles);
   p.status = h->status;
-  const int grid = static_cast<int>(tiles < h->sm_count ? tiles : h->sm_count);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (split) mlp_chain_kernel<32, true><<<grid, kThreads, Cfg<32, true>::kSmemBytes, s>>>(p);
-  else mlp_chain_kernel<64, false><<<grid, kThreads, Cfg<64, false>::kSmemBytes, s>>>(p);
+  if (split) {
+    const int grid = static_cast<int>(tiles < h->sm_count ? tiles : h->sm_count);
+    mlp_chain_kernel<32, true><<<grid, kThreads, Cfg<32, true>::kSmemBytes, s>>>(p);
+  } else {
+    // one cluster of two CTAs per tile of 128 queries, at most one cluster per SM pair
+    const int pairs = static_cast<int>(tiles < h->sm_count / 2 ? tiles : h->sm_count / 2);
+    mlp_chain_pair_kernel<<<2 * pairs, kThreads, kPairSmemBytes, s>>>(p);
+  }
   HB_CUDA_TRY(cudaGetLastError());
   return HB_OK;
 }
