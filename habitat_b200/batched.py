@@ -236,6 +236,14 @@ class MLPHandle:
         code = ctypes.c_int32(0)
         _native.check(_native.load().hb_mlp_status(self._handle, ctypes.byref(code)))
 
+    def phase_cycles(self):
+        """{wait, epilogue, fc2, layers} cycle counters of the last bf16 launch (synchronises)."""
+        out = (ctypes.c_int64 * 16)()
+        _native.check(_native.load().hb_mlp_phase_cycles(self._handle, out))
+        names = ("wait", "epilogue", "fc2", "layers", "mma_wait_act", "mma_wait_own", "mma_wait_peer",
+                 "mma_issue", "slots", "producer_wait_slot", "producer_copy", "copies")
+        return dict(zip(names, [int(x) for x in out]))
+
     def close(self):
         if self._handle:
             _native.load().hb_mlp_destroy(self._handle)

@@ -91,6 +91,7 @@ struct MlpParams {
   float* out;                // [Q]
   int32_t num_tiles;
   int32_t* status;           // device word: 0 ok, else (role << 8 | site)
+  long long* phase_cycles;   // [4] cluster 0, leader: cycles waiting for MMAs, in hidden epilogues, in fc2; layers
 };
 
 // ---------------------------------------------------------------------------
@@ -504,8 +505,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
 //     queries 64 c .. 64 c + 63; its TMEM receives the D rows of its features
 //     for all 128 queries.  Each weight byte is fetched once per pair.
 //   * The leader CTA (rank 0) issues every MMA.  A ring slot is ready when the
-//     leader's own bulk copy and the peer's have landed; the peer relays the
-//     completion of its copy with a remote mbarrier arrive.  tcgen05.commit
+//     leader's own bulk copy and the peer's have landed; each producer of the
+//     peer forwards the completion of its copy with a remote mbarrier arrive
+//     (one forwarding thread for all slots was measured to cap the ring at one
+//     slot per ~1100 cycles).  tcgen05.commit
 //     multicasts "slot free" and "layer done" to both CTAs.
 //   * The epilogue of CTA c holds features x all 128 queries, but the next
 //     layer needs, in each CTA, all features x its 64 queries: half of the
@@ -536,6 +539,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                : "memory");
+}
+// Remote arrive without cluster-scope release: used to forward "my bulk copy
+// landed", where the data was written by the async proxy into this CTA's own
+// shared memory and is read there by this CTA's own tensor core.
+__device__ __forceinline__ void mbar_arrive_remote_plain(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -653,7 +662,6 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
   const int pair_id = static_cast<int>(blockIdx.x >> 1);
   int my_tiles = 0;
   if (pair_id < p.num_tiles) my_tiles = (p.num_tiles - 1 - pair_id) / n_pairs + 1;
-  const uint32_t loads_per_tile = static_cast<uint32_t>(kPairMT + p.layers * kPairMT * kNumKB);
 
   uint32_t issued = 0;
 
@@ -665,6 +673,9 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
       const uint32_t w = static_cast<uint32_t>(warp - 6);
       uint32_t it = 0;
       bool ok = true;
+      const bool ptimed = p.phase_cycles != nullptr && blockIdx.x == 0 && w == 0;
+      const uint32_t peer_full_leader = map_to_cta(bar_peer_full + 8 * w, 0);
+      long long pc_empty = 0, pc_copy = 0, pc_n = 0;
       for (int t = 0; t < my_tiles && ok; ++t) {
         size_t layer_base = 0;   // in tile images
         for (int L = 0; L < n_layers && ok; ++L) {
@@ -674,16 +685,28 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
             for (int kb = 0; kb < nkb; ++kb, ++it) {
               if (it % kPairStages != w) continue;
               const uint32_t ph = (it / kPairStages) & 1u;
+              const long long q0 = ptimed ? clock64() : 0;
               if (!mbar_wait(bar_empty + 8 * w, ph ^ 1u, abort_flag, p.status, 0x111)) { ok = false; break; }
+              const long long q1 = ptimed ? clock64() : 0;
               mbar_expect_tx(bar_full + 8 * w, kTileBytes);
               bulk_g2s(stage0 + w * kTileBytes, p.wpack + (blk + kb) * kTileBytes, kTileBytes,
                        bar_full + 8 * w);
               issued = it + 1;
+              if (rank == 1) {
+                // the leader issues the MMAs: tell it when this CTA's half has landed
+                if (!mbar_wait(bar_full + 8 * w, ph, abort_flag, p.status, 0x112)) { ok = false; break; }
+                mbar_arrive_remote_plain(peer_full_leader);
+              }
+              if (ptimed) {
+                mbar_wait(bar_full + 8 * w, ph, abort_flag, p.status, 0x112);
+                pc_empty += q1 - q0; pc_copy += clock64() - q1; ++pc_n;
+              }
             }
           }
           layer_base += static_cast<size_t>(kNumMT) * nkb;
         }
       }
+      if (ptimed) { p.phase_cycles[9] = pc_empty; p.phase_cycles[10] = pc_copy; p.phase_cycles[11] = pc_n; }
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
@@ -697,19 +720,23 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
       const uint32_t b_lo0 = (act & 0x3FFFF) >> 4;
       uint32_t s = 0, ph = 0, lay = 0;
       bool ok = true;
+      const bool mtimed = p.phase_cycles != nullptr && blockIdx.x == 0;
+      long long mc_act = 0, mc_full = 0, mc_peer = 0, mc_issue = 0, mc_n = 0;
       for (int t = 0; t < my_tiles && ok; ++t) {
         for (int L = 0; L < n_layers && ok; ++L, ++lay) {
+          const long long m0 = mtimed ? clock64() : 0;
           if (!mbar_wait_cluster(bar_act, lay & 1u, abort_flag, p.status, 0x211)) { ok = false; break; }
           tc_fence_after();
+          if (mtimed) mc_act += clock64() - m0;
           const int nkb = L == 0 ? 1 : kNumKB;
           for (int j = 0; j < kPairMT && ok; ++j) {
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(j * kPairQ);
             for (int kb = 0; kb < nkb; ++kb) {
-              if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x212) ||
-                  !mbar_wait_cluster(bar_peer_full + 8 * s, ph, abort_flag, p.status, 0x213)) {
-                ok = false;
-                break;
-              }
+              const long long m1 = mtimed ? clock64() : 0;
+              if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x212)) { ok = false; break; }
+              const long long m2 = mtimed ? clock64() : 0;
+              if (!mbar_wait_cluster(bar_peer_full + 8 * s, ph, abort_flag, p.status, 0x213)) { ok = false; break; }
+              const long long m3 = mtimed ? clock64() : 0;
               tc_fence_after();
               const uint64_t a0 = desc_hi | (a_lo0 + s * (kTileBytes >> 4));
               const uint64_t b0 = desc_hi | (b_lo0 + static_cast<uint32_t>(kb) * (kPairActKb >> 4));
@@ -718,21 +745,16 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
               tc_mma_pair_bf16(d_tmem, a0 + 4, b0 + 4, idesc, 1u);
               tc_mma_pair_bf16(d_tmem, a0 + 6, b0 + 6, idesc, 1u);
               tc_commit_pair(bar_empty + 8 * s);
+              if (mtimed) { mc_full += m2 - m1; mc_peer += m3 - m2; mc_issue += clock64() - m3; ++mc_n; }
               if (++s == kPairStages) { s = 0; ph ^= 1u; }
             }
           }
           if (ok) tc_commit_pair(bar_acc);
         }
       }
-    } else if (lane == 0 && rank == 1) {
-      // ------------------------------ relay (peer) --------------------------
-      // Tells the leader that this CTA's half of a ring slot has landed.
-      const uint32_t total = loads_per_tile * static_cast<uint32_t>(my_tiles);
-      uint32_t s = 0, ph = 0;
-      for (uint32_t it = 0; it < total; ++it) {
-        if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x411)) break;
-        mbar_arrive_remote(map_to_cta(bar_peer_full + 8 * s, 0));
-        if (++s == kPairStages) { s = 0; ph ^= 1u; }
+      if (mtimed) {
+        p.phase_cycles[4] = mc_act; p.phase_cycles[5] = mc_full; p.phase_cycles[6] = mc_peer;
+        p.phase_cycles[7] = mc_issue; p.phase_cycles[8] = mc_n;
       }
     }
   } else if (warp >= 2) {
@@ -747,6 +769,8 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
     uint32_t lay = 0, tile_no = 0;
     bool ok = true;
     float* red = reinterpret_cast<float*>(base_ptr);   // [128][65], aliases activations
+    const bool timed = p.phase_cycles != nullptr && blockIdx.x == 0 && e == 0;
+    long long c_wait = 0, c_epi = 0, c_fc2 = 0, c_layers = 0;
 
     for (int t = 0; t < my_tiles && ok; ++t, ++tile_no) {
       const int tile = pair_id + t * n_pairs;
@@ -787,10 +811,12 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
       }
 
       for (int L = 0; L < n_layers && ok; ++L, ++lay) {
+        const long long c0 = timed ? clock64() : 0;
         if (e == 0) *epi_ok = mbar_wait(bar_acc, lay & 1u, abort_flag, p.status, 0x311) ? 1 : 0;
         epi_bar_sync();
         if (*epi_ok == 0) { ok = false; break; }
         tc_fence_after();
+        const long long c1 = timed ? clock64() : 0;
         const float* bias = p.bias + L * kWidth;
         const bool last = (L == n_layers - 1);
         if (!last) {
@@ -822,6 +848,7 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
             if (rank == 0) mbar_arrive(bar_act);
             else mbar_arrive_remote(bar_act_leader);
           }
+          if (timed) { c_wait += c1 - c0; c_epi += clock64() - c1; ++c_layers; }
         } else {
           // fc2 over this CTA's 512 features, 64 queries at a time
 #pragma unroll 1
@@ -872,8 +899,13 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
             if (q < p.Q) p.out[q] = fc2_mine[e] + fc2_peer[e] + p.fc2_b;
           }
           epi_bar_sync();
+          if (timed) { c_wait += c1 - c0; c_fc2 += clock64() - c1; ++c_layers; }
         }
       }
+    }
+    if (timed) {
+      p.phase_cycles[0] = c_wait; p.phase_cycles[1] = c_epi;
+      p.phase_cycles[2] = c_fc2; p.phase_cycles[3] = c_layers;
     }
   }
 
@@ -931,12 +963,13 @@ struct hb_mlp {
   double* sigma = nullptr;
   double* dev_feat = nullptr;
   int32_t* status = nullptr;
+  long long* phase_cycles = nullptr;
 };
 
 extern "C" void hb_mlp_destroy(hb_mlp* h) {
   if (!h) return;
   cudaFree(h->wpack); cudaFree(h->bias); cudaFree(h->fc2_w); cudaFree(h->mu);
-  cudaFree(h->sigma); cudaFree(h->dev_feat); cudaFree(h->status);
+  cudaFree(h->sigma); cudaFree(h->dev_feat); cudaFree(h->status); cudaFree(h->phase_cycles);
   delete h;
 }
 
@@ -1025,6 +1058,9 @@ extern "C" hb_status hb_mlp_create(hb_mlp** handle, int32_t n_op_features, int32
   if ((e = cudaMalloc(reinterpret_cast<void**>(&h->status), sizeof(int32_t))) != cudaSuccess)
     return fail(e, "cudaMalloc status");
   if ((e = cudaMemset(h->status, 0, sizeof(int32_t))) != cudaSuccess) return fail(e, "cudaMemset");
+  if ((e = cudaMalloc(reinterpret_cast<void**>(&h->phase_cycles), 16 * sizeof(long long))) != cudaSuccess)
+    return fail(e, "cudaMalloc phase_cycles");
+  if ((e = cudaMemset(h->phase_cycles, 0, 16 * sizeof(long long))) != cudaSuccess) return fail(e, "cudaMemset");
   e = cudaFuncSetAttribute(mlp_chain_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kPairSmemBytes);
   if (e != cudaSuccess) return fail(e, "cudaFuncSetAttribute");
@@ -1055,6 +1091,7 @@ extern "C" hb_status hb_mlp_predict(hb_mlp* h, const float* op_features, const u
   p.n_op_feat = h->n_op_feat; p.layers = h->layers; p.feats = op_features;
   p.dev_row = device_row; p.Q = Q; p.out = out; p.num_tiles = static_cast<int32_t>(tiles);
   p.status = h->status;
+  p.phase_cycles = h->phase_cycles;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (split) {
     const int grid = static_cast<int>(tiles < h->sm_count ? tiles : h->sm_count);
@@ -1078,6 +1115,17 @@ extern "C" hb_status hb_mlp_status(hb_mlp* h, int32_t* device_status) {
     hb::set_error("mlp kernel: a bounded device-side wait ran out (site 0x%x)", *device_status);
     return HB_ERR_DEVICE_TIMEOUT;
   }
+  return HB_OK;
+}
+
+extern "C" hb_status hb_mlp_phase_cycles(hb_mlp* h, int64_t out[16]) {
+  if (!h || !out) {
+    hb::set_error("hb_mlp_phase_cycles: NULL argument");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  long long v[16];
+  HB_CUDA_TRY(cudaMemcpy(v, h->phase_cycles, sizeof(v), cudaMemcpyDeviceToHost));
+  for (int i = 0; i < 16; ++i) out[i] = v[i];
   return HB_OK;
 }
 
