@@ -197,6 +197,14 @@ hb_status hb_mlp_predict(hb_mlp* handle, const float* op_features, const uint8_t
  * counterpart: the reference's predict() is host code. */
 hb_status hb_mlp_status(hb_mlp* handle, int32_t* device_status);
 
+/* Profiling aid (bf16 kernel): SM cycle counters of the first cluster's leader CTA
+ * for the most recent launch.  out[0..3] epilogue: waiting for a layer's MMAs,
+ * draining hidden layers, fc2, layers counted.  out[4..8] MMA issuer: waiting for
+ * activations, for its own weight copy, for the peer's, issuing, ring slots
+ * counted.  out[9..11] first producer: waiting for a free slot, copy latency,
+ * copies counted.  Synchronises.  No reference counterpart. */
+hb_status hb_mlp_phase_cycles(hb_mlp* handle, int64_t out[16]);
+
 /* Host-buffer form of hb_mlp_predict; also checks hb_mlp_status. */
 hb_status hb_mlp_predict_host(hb_mlp* handle, const float* op_features,
                               const uint8_t* device_row, int64_t Q, float* out);
