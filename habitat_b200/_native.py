@@ -95,6 +95,8 @@ EXPORTS = {
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),
     "hb_plane_sum": (ctypes.c_int32, [
         ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "hb_plane_sum_static": (ctypes.c_int32, [
+        ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
 }
 
 _lib = None

@@ -158,3 +158,60 @@ extern "C" hb_status hb_special_scale(const float* run_time_ms, const float* pre
   HB_CUDA_TRY(cudaGetLastError());
   return HB_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Plane sums for callers that must not allocate
+// ---------------------------------------------------------------------------
+// hb_plane_sum above keeps its stage-1 partial sums in a buffer it obtains with
+// cudaMalloc on first use.  Some hosts cannot tolerate that: a serving process
+// that hands the whole device to its own memory pool at start-up (a later
+// driver allocation fails or fragments the pool), or one whose latency rules
+// forbid driver allocations once initialisation is over.  For them the same two
+// kernels run on a scratch array that is part of the library image: it occupies
+// kStaticPlanes * kPlaneBlocks * 8 bytes = 128 KB on every GPU that loads the
+// library, from load until the process exits.
+constexpr int kStaticPlanes = 64;
+static __device__ __align__(256) double g_static_partial[kStaticPlanes * kPlaneBlocks];
+
+namespace {
+constexpr int kMaxCudaDevices = 64;
+// Device address of g_static_partial on each device, resolved on first use.  In
+// host code the symbol's name is only a handle for the runtime, not an address a
+// kernel could dereference, hence the look-up.
+double* g_static_partial_ptr[kMaxCudaDevices] = {};
+}  // namespace
+
+extern "C" hb_status hb_plane_sum_static(const float* values, int64_t plane_len, int32_t n_planes,
+                                         double* out, void* stream) {
+  if (plane_len < 0 || n_planes < 0 || (n_planes > 0 && (!values || !out))) {
+    hb::set_error("hb_plane_sum_static: bad arguments");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  if (n_planes > kStaticPlanes) {
+    hb::set_error("hb_plane_sum_static: %d planes requested, the built-in scratch holds %d "
+                  "(use hb_plane_sum, or split the call)", n_planes, kStaticPlanes);
+    return HB_ERR_TOO_LARGE;
+  }
+  if (n_planes == 0) return HB_OK;
+  int dev = 0;
+  HB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxCudaDevices) {
+    hb::set_error("hb_plane_sum_static: device ordinal %d out of range", dev);
+    return HB_ERR_UNSUPPORTED;
+  }
+  if (!g_static_partial_ptr[dev]) {
+    // once per device, with that device current
+    void* ptr = nullptr;
+    HB_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_partial));
+    g_static_partial_ptr[dev] = static_cast<double*>(ptr);
+  }
+  double* scratch = g_static_partial_ptr[dev];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // Stage 1 writes every partial that stage 2 reads, so nothing in the scratch
+  // has to start at zero; whatever the previous call left there is overwritten.
+  plane_partial_kernel<<<dim3(kPlaneBlocks, n_planes), kSumThreads, 0, s>>>(values, plane_len, scratch);
+  HB_CUDA_TRY(cudaGetLastError());
+  plane_final_kernel<<<n_planes, kSumThreads, 0, s>>>(scratch, out);
+  HB_CUDA_TRY(cudaGetLastError());
+  return HB_OK;
+}

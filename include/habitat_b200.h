@@ -234,6 +234,22 @@ hb_status hb_segment_sum(const float* values, const int64_t* offsets, int64_t n_
 hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_t n_planes, double* out,
                        void* stream);
 
+/* hb_plane_sum for callers that must not allocate device memory after start-up
+ * (a process that gave the whole GPU to its own memory pool, or one that
+ * forbids driver allocations once it is serving).  Same arguments and results
+ * as hb_plane_sum, but the partial sums live in a 128 KB array built into the
+ * library image (held on every GPU that loads the library until the process
+ * exits) and the call performs no cudaMalloc / cudaFree.
+ *   - n_planes <= 64; more is refused with HB_ERR_TOO_LARGE.
+ *   - The first call on each device resolves the array's device address (the
+ *     device must be current); make that call during set-up, before any stream
+ *     capture is begun.
+ *   - All calls on a device share the one array: calls whose kernels may run
+ *     at the same time (different streams) race; serialise them.
+ * It has no counterpart in the reference, whose totals are host-side sums. */
+hb_status hb_plane_sum_static(const float* values, int64_t plane_len, int32_t n_planes, double* out,
+                              void* stream);
+
 #ifdef __cplusplus
 }
 #endif
