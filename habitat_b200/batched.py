@@ -241,7 +241,8 @@ class MLPHandle:
         out = (ctypes.c_int64 * 16)()
         _native.check(_native.load().hb_mlp_phase_cycles(self._handle, out))
         names = ("wait", "epilogue", "fc2", "layers", "mma_wait_act", "mma_wait_own", "mma_wait_peer",
-                 "mma_issue", "slots", "producer_wait_slot", "producer_copy", "copies")
+                 "mma_issue", "slots", "producer_wait_slot", "producer_copy", "copies", "epi_tmem_load",
+                 "epi_bias_load", "epi_publish", "epi_remote")
         return dict(zip(names, [int(x) for x in out]))
 
     def close(self):

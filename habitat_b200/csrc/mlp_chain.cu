@@ -173,6 +173,34 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 lanes x 64 consecutive 32-bit columns in one instruction: halves the number of
+// load round trips of the epilogue (each tcgen05.ld + wait costs several hundred cycles).
+__device__ __forceinline__ void tc_ld64(uint32_t taddr, float (&v)[64]) {
+  uint32_t r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+        "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]),
+        "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]),
+        "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]),
+        "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+        "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]),
+        "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows are 128 B
 // apart, groups of 8 rows 1024 B apart (the stride byte offset); the leading
 // byte offset is unused for swizzled K-major operands; descriptor version 1.
@@ -510,6 +538,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
 //     (one forwarding thread for all slots was measured to cap the ring at one
 //     slot per ~1100 cycles).  tcgen05.commit
 //     multicasts "slot free" and "layer done" to both CTAs.
+//   * The activations are the MN-major B operand here (one 128-byte row of 64
+//     queries per K index): an epilogue thread owns one feature = one K row
+//     and writes eight queries per 16-byte store.
 //   * The epilogue of CTA c holds features x all 128 queries, but the next
 //     layer needs, in each CTA, all features x its 64 queries: half of the
 //     bf16 results are stored into the peer's shared memory (st.shared::cluster).
@@ -523,9 +554,13 @@ constexpr int kPairMT = kWidth / 256;       // 4 MMA row blocks per layer
 constexpr int kPairStages = 6;
 constexpr int kPairActKb = kPairHalfQ * 128;          // 8 KB per K block
 constexpr int kPairActBytes = kNumKB * kPairActKb;    // 128 KB
+constexpr int kPairThreads = 512;              // warps: 0 alloc, 1 MMA, 2-5 + 12-15 epilogue, 6-11 producers
 constexpr int kPairSmemBytes = kPairActBytes + kPairStages * kTileBytes + 1024 + 1024;
 static_assert(kPairSmemBytes <= 232448, "over the 227 KB shared-memory limit");
 
+__device__ __forceinline__ void pair_epi_bar_sync() {
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -574,10 +609,21 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     }
   }
 }
-__device__ __forceinline__ void st_cluster_b16(uint32_t cluster_addr, __nv_bfloat16 v) {
-  asm volatile("st.shared::cluster.b16 [%0], %1;" ::"r"(cluster_addr),
-               "h"(__bfloat16_as_ushort(v))
-               : "memory");
+// Asynchronous 16-byte store into a peer CTA's shared memory; completion is counted
+// in bytes on an mbarrier of that CTA.  Unlike st.shared::cluster the issuing
+// thread does not wait for the store to be acknowledged.
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c,
+                                            uint32_t d, uint32_t cluster_mbar) {
+  asm volatile(
+      "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+      ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(cluster_mbar)
+      : "memory");
+}
+// Byte offset of element (K row k, query n) of an MN-major, 128-byte-swizzled B
+// operand holding 64 queries per row: rows are 128 B apart, the eight 16-byte
+// groups of a row are permuted by the row index modulo 8.
+__device__ __forceinline__ uint32_t mn_off(uint32_t k, uint32_t n) {
+  return k * 128u + ((((n >> 3) ^ k) & 7u) << 4) + ((n & 7u) << 1);
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
@@ -603,7 +649,7 @@ __device__ __forceinline__ void tc_mma_pair_bf16(uint32_t d_tmem, uint64_t a_des
       : "memory");
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -615,15 +661,15 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
   const uint32_t bars = stage0 + kPairStages * kTileBytes;
   uint8_t* bars_ptr = base_ptr + (bars - base);
   // barrier block (same offsets in both CTAs)
-  const uint32_t bar_full = bars;                          // [stages] own bulk copy landed
-  const uint32_t bar_peer_full = bars + 8 * kPairStages;   // [stages] leader only: peer's copy landed
+  const uint32_t bar_full = bars;                          // [stages] weight halves landed (leader: both CTAs')
   const uint32_t bar_empty = bars + 16 * kPairStages;      // [stages] slot consumed (multicast commit)
   const uint32_t bar_acc = bars + 24 * kPairStages;        // layer accumulated (multicast commit)
   const uint32_t bar_act = bar_acc + 8;                    // leader only: both epilogues done
   const uint32_t bar_fc2 = bar_acc + 16;                   // peer's fc2 partial sums arrived
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 24 * kPairStages + 24);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 24 * kPairStages + 28);
-  volatile int* epi_ok = reinterpret_cast<volatile int*>(bars_ptr + 24 * kPairStages + 32);
+  const uint32_t bar_in = bar_acc + 24;                    // peer's half of the next activations landed (bytes)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 24 * kPairStages + 40);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 24 * kPairStages + 44);
+  volatile int* epi_ok = reinterpret_cast<volatile int*>(bars_ptr + 24 * kPairStages + 48);
   float* fc2_mine = reinterpret_cast<float*>(bars_ptr + 512);    // [64] own queries, own features
   float* fc2_peer = reinterpret_cast<float*>(bars_ptr + 768);    // [64] own queries, peer's features
 
@@ -634,13 +680,14 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
 
   if (threadIdx.x == 32) {
     for (int s = 0; s < kPairStages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_peer_full + 8 * s, 1);
+      // leader: own arrive.expect_tx + the peer's forwarded arrive; peer: its own only
+      mbar_init(bar_full + 8 * s, rank == 0 ? 2 : 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_acc, 1);
     mbar_init(bar_act, 2);
     mbar_init(bar_fc2, 1);
+    mbar_init(bar_in, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -665,7 +712,7 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
 
   uint32_t issued = 0;
 
-  if (warp >= 6) {
+  if (warp >= 6 && warp < 12) {
     // ------------------------------ producers -----------------------------
     // One producer per ring slot.  The pack is laid out per 128-feature block
     // (layer -> block -> K block); this CTA streams blocks 2 j + rank.
@@ -674,7 +721,7 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
       uint32_t it = 0;
       bool ok = true;
       const bool ptimed = p.phase_cycles != nullptr && blockIdx.x == 0 && w == 0;
-      const uint32_t peer_full_leader = map_to_cta(bar_peer_full + 8 * w, 0);
+      const uint32_t peer_full_leader = map_to_cta(bar_full + 8 * w, 0);
       long long pc_empty = 0, pc_copy = 0, pc_n = 0;
       for (int t = 0; t < my_tiles && ok; ++t) {
         size_t layer_base = 0;   // in tile images
@@ -711,7 +758,8 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       // ------------------------------ MMA issuer (leader) -------------------
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+      // D fp32, A/B bf16, A K-major, B MN-major (bit 16), N = 128, M = 256
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                  (static_cast<uint32_t>(kPairQ >> 3) << 17) |
                                  (static_cast<uint32_t>(256 >> 4) << 24);
       const uint64_t desc_hi = (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) |
@@ -733,17 +781,17 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(j * kPairQ);
             for (int kb = 0; kb < nkb; ++kb) {
               const long long m1 = mtimed ? clock64() : 0;
-              if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x212)) { ok = false; break; }
+              if (!mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, 0x212)) { ok = false; break; }
               const long long m2 = mtimed ? clock64() : 0;
-              if (!mbar_wait_cluster(bar_peer_full + 8 * s, ph, abort_flag, p.status, 0x213)) { ok = false; break; }
-              const long long m3 = mtimed ? clock64() : 0;
+              const long long m3 = m2;
               tc_fence_after();
               const uint64_t a0 = desc_hi | (a_lo0 + s * (kTileBytes >> 4));
               const uint64_t b0 = desc_hi | (b_lo0 + static_cast<uint32_t>(kb) * (kPairActKb >> 4));
+              // a K step of 16: 32 bytes along an A row, 16 K rows (2 KB) of B
               tc_mma_pair_bf16(d_tmem, a0, b0, idesc, kb != 0 ? 1u : 0u);
-              tc_mma_pair_bf16(d_tmem, a0 + 2, b0 + 2, idesc, 1u);
-              tc_mma_pair_bf16(d_tmem, a0 + 4, b0 + 4, idesc, 1u);
-              tc_mma_pair_bf16(d_tmem, a0 + 6, b0 + 6, idesc, 1u);
+              tc_mma_pair_bf16(d_tmem, a0 + 2, b0 + 128, idesc, 1u);
+              tc_mma_pair_bf16(d_tmem, a0 + 4, b0 + 256, idesc, 1u);
+              tc_mma_pair_bf16(d_tmem, a0 + 6, b0 + 384, idesc, 1u);
               tc_commit_pair(bar_empty + 8 * s);
               if (mtimed) { mc_full += m2 - m1; mc_peer += m3 - m2; mc_issue += clock64() - m3; ++mc_n; }
               if (++s == kPairStages) { s = 0; ph ^= 1u; }
@@ -759,25 +807,31 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
     }
   } else if (warp >= 2) {
     // ------------------------------ epilogue ------------------------------
-    const int e = threadIdx.x - 64;            // 0..127
+    // Two groups of four warps (warps 2-5 and 12-15); a warp may only read the
+    // TMEM lane quadrant (warp id mod 4).  Group g drains the 256-feature blocks
+    // 2 g and 2 g + 1 of a layer, so both halves of TMEM are read at once.
+    const int grp = warp >= 12 ? 1 : 0;
+    const int e = (warp - (grp ? 12 : 2)) * 32 + lane;   // 0..127 inside the group
+    const int T = grp * 128 + e;                         // 0..255 over both groups
     const int quad = warp & 3;
     const int r = quad * 32 + lane;            // feature row inside this CTA's 128-row block
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const int C_in = p.n_op_feat + 4;
     const uint32_t act_peer = map_to_cta(act, peer);
     const uint32_t bar_act_leader = map_to_cta(bar_act, 0);
-    uint32_t lay = 0, tile_no = 0;
+    const uint32_t bar_in_peer = map_to_cta(bar_in, peer);
+    uint32_t lay = 0, tile_no = 0, in_phase = 0;
     bool ok = true;
-    float* red = reinterpret_cast<float*>(base_ptr);   // [128][65], aliases activations
-    const bool timed = p.phase_cycles != nullptr && blockIdx.x == 0 && e == 0;
-    long long c_wait = 0, c_epi = 0, c_fc2 = 0, c_layers = 0;
+    float* red = reinterpret_cast<float*>(base_ptr);   // [256][33], aliases activations
+    const bool timed = p.phase_cycles != nullptr && blockIdx.x == 0 && T == 0;
+    long long c_wait = 0, c_epi = 0, c_fc2 = 0, c_layers = 0, c_ld = 0, c_bias = 0, c_sync = 0, c_loc = 0, c_rem = 0;
 
     for (int t = 0; t < my_tiles && ok; ++t, ++tile_no) {
       const int tile = pair_id + t * n_pairs;
       const int64_t q0 = static_cast<int64_t>(tile) * kPairQ + static_cast<int64_t>(rank) * kPairHalfQ;
 
-      if (e < kPairHalfQ) {
-        const int64_t q = q0 + e;
+      if (T < kPairHalfQ) {
+        const int64_t q = q0 + T;
         __nv_bfloat16 row[kKBlk];
 #pragma unroll
         for (int c = 0; c < kKBlk; ++c) row[c] = __float2bfloat16_rn(0.0f);
@@ -796,109 +850,126 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
             row[2 * C_in + c] = hi;
           }
         }
-        const uint4* src = reinterpret_cast<const uint4*>(row);
+        // column T of K rows 0..63 (row k, query n: 128 k + 16 ((n / 8) xor (k mod 8)) + 2 (n mod 8))
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          uint4* dst = reinterpret_cast<uint4*>(base_ptr + e * 128 + (((ch ^ e) & 7) << 4));
-          *dst = src[ch];
-        }
+        for (int c = 0; c < kKBlk; ++c)
+          *reinterpret_cast<__nv_bfloat16*>(base_ptr + mn_off(static_cast<uint32_t>(c), static_cast<uint32_t>(T))) = row[c];
       }
       fence_proxy_async();
-      epi_bar_sync();
-      if (e == 0) {
+      pair_epi_bar_sync();
+      if (T == 0) {
         if (rank == 0) mbar_arrive(bar_act);
         else mbar_arrive_remote(bar_act_leader);
       }
 
       for (int L = 0; L < n_layers && ok; ++L, ++lay) {
         const long long c0 = timed ? clock64() : 0;
-        if (e == 0) *epi_ok = mbar_wait(bar_acc, lay & 1u, abort_flag, p.status, 0x311) ? 1 : 0;
-        epi_bar_sync();
+        if (T == 0) *epi_ok = mbar_wait(bar_acc, lay & 1u, abort_flag, p.status, 0x311) ? 1 : 0;
+        pair_epi_bar_sync();
         if (*epi_ok == 0) { ok = false; break; }
         tc_fence_after();
         const long long c1 = timed ? clock64() : 0;
         const float* bias = p.bias + L * kWidth;
         const bool last = (L == n_layers - 1);
         if (!last) {
+          // the peer sends 512 K rows x 128 B of next-layer activations into this CTA
+          if (T == 0) mbar_expect_tx(bar_in, 512u * 128u);
 #pragma unroll 1
-          for (int j = 0; j < kPairMT; ++j) {
+          for (int jj = 0; jj < 2; ++jj) {
+            const int j = grp * 2 + jj;
             const int f = j * 256 + static_cast<int>(rank) * 128 + r;   // feature = next layer's K index
+            const long long d0 = timed ? clock64() : 0;
             const float b = __ldg(bias + f);
-            const uint32_t kb_off = static_cast<uint32_t>(f >> 6) * kPairActKb;
-            const uint32_t col = static_cast<uint32_t>(f & 63);
+            if (timed) { c_bias += clock64() - d0 + static_cast<long long>(b == 12345.0f); }
+            const uint32_t row_off = static_cast<uint32_t>(f) * 128u;   // K row f of the next layer's B operand
+            const uint32_t sw = static_cast<uint32_t>(f) & 7u;
 #pragma unroll
-            for (int h = 0; h < kPairQ / 32; ++h) {
-              float v[32];
-              tc_ld32(t_lane + static_cast<uint32_t>(j * kPairQ + h * 32), v);
-              const bool mine = static_cast<uint32_t>(h >> 1) == rank;   // queries 64 (h / 2) ..
+            for (int h = 0; h < 2; ++h) {            // 64 queries = one CTA's share per load
+              float v[64];
+              const long long d1 = timed ? clock64() : 0;
+              tc_ld64(t_lane + static_cast<uint32_t>(j * kPairQ + h * 64), v);
+              if (timed) c_ld += clock64() - d1;
+              const bool mine = static_cast<uint32_t>(h) == rank;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const uint32_t n = static_cast<uint32_t>((h & 1) * 32 + i);   // row in the owner's buffer
-                const __nv_bfloat16 hi = __float2bfloat16_rn(fmaxf(v[i] + b, 0.0f));
-                const uint32_t off = kb_off + swz_off(n, col);
-                if (mine) *reinterpret_cast<__nv_bfloat16*>(base_ptr + off) = hi;
-                else st_cluster_b16(act_peer + off, hi);
+              for (int g = 0; g < 8; ++g) {          // eight queries per 16-byte store
+                uint32_t w4[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const __nv_bfloat162 pk = __floats2bfloat162_rn(fmaxf(v[g * 8 + 2 * u] + b, 0.0f),
+                                                                  fmaxf(v[g * 8 + 2 * u + 1] + b, 0.0f));
+                  w4[u] = *reinterpret_cast<const uint32_t*>(&pk);
+                }
+                const uint32_t off = row_off + ((static_cast<uint32_t>(g) ^ sw) << 4);
+                if (mine) *reinterpret_cast<uint4*>(base_ptr + off) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                else st_async_v4(act_peer + off, w4[0], w4[1], w4[2], w4[3], bar_in_peer);
               }
+              if (timed) { if (mine) c_loc += clock64() - d1; else c_rem += clock64() - d1; }
             }
           }
+          const long long d2 = timed ? clock64() : 0;
           tc_fence_before();
           asm volatile("fence.proxy.async;" ::: "memory");   // local and peer shared memory
-          epi_bar_sync();
-          if (e == 0) {
-            if (rank == 0) mbar_arrive(bar_act);
-            else mbar_arrive_remote(bar_act_leader);
+          pair_epi_bar_sync();
+          if (T == 0) {
+            // own stores are fenced above; the peer's arrive as counted bytes
+            if (mbar_wait_cluster(bar_in, in_phase, abort_flag, p.status, 0x313)) {
+              if (rank == 0) mbar_arrive(bar_act);
+              else mbar_arrive_remote(bar_act_leader);
+            }
           }
-          if (timed) { c_wait += c1 - c0; c_epi += clock64() - c1; ++c_layers; }
+          in_phase ^= 1u;
+          if (timed) { c_wait += c1 - c0; c_epi += clock64() - c1; ++c_layers; c_sync += clock64() - d2; }
         } else {
-          // fc2 over this CTA's 512 features, 64 queries at a time
+          // fc2 over this CTA's 512 features, 32 queries at a time
 #pragma unroll 1
-          for (int half = 0; half < 2; ++half) {
-            float acc[kPairHalfQ];
+          for (int qd = 0; qd < 4; ++qd) {
+            float acc[32];
 #pragma unroll
-            for (int i = 0; i < kPairHalfQ; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
 #pragma unroll 1
-            for (int j = 0; j < kPairMT; ++j) {
+            for (int jj = 0; jj < 2; ++jj) {
+              const int j = grp * 2 + jj;
               const int f = j * 256 + static_cast<int>(rank) * 128 + r;
               const float b = __ldg(bias + f);
               const float w = __ldg(p.fc2_w + f);
+              float v[32];
+              tc_ld32(t_lane + static_cast<uint32_t>(j * kPairQ + qd * 32), v);
 #pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                float v[32];
-                tc_ld32(t_lane + static_cast<uint32_t>(j * kPairQ + half * 64 + h * 32), v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  acc[h * 32 + i] = fmaf(w, fmaxf(v[i] + b, 0.0f), acc[h * 32 + i]);
-              }
+              for (int i = 0; i < 32; ++i) acc[i] = fmaf(w, fmaxf(v[i] + b, 0.0f), acc[i]);
             }
+            const int row = grp * 128 + r;
 #pragma unroll
-            for (int i = 0; i < kPairHalfQ; ++i) red[r * (kPairHalfQ + 1) + i] = acc[i];
-            epi_bar_sync();
-            const int n = e & 63, part = e >> 6;
-            float s = 0.0f;
-            for (int k = 0; k < 64; ++k) s += red[(part * 64 + k) * (kPairHalfQ + 1) + n];
-            epi_bar_sync();
-            red[part * 64 + n] = s;
-            epi_bar_sync();
-            if (e < kPairHalfQ) {
-              const float tot = red[e] + red[64 + e];
-              if (static_cast<uint32_t>(half) == rank) fc2_mine[e] = tot;
-              else st_cluster_f32(map_to_cta(smem_u32(fc2_peer + e), peer), tot);
+            for (int i = 0; i < 32; ++i) red[row * 33 + i] = acc[i];
+            pair_epi_bar_sync();
+            const int n = T & 31, part = T >> 5;       // 8 parts of 32 feature rows each
+            float sum = 0.0f;
+            for (int k2 = 0; k2 < 32; ++k2) sum += red[(part * 32 + k2) * 33 + n];
+            pair_epi_bar_sync();
+            red[part * 32 + n] = sum;
+            pair_epi_bar_sync();
+            if (T < 32) {
+              float tot = 0.0f;
+#pragma unroll
+              for (int k2 = 0; k2 < 8; ++k2) tot += red[k2 * 32 + T];
+              const int slot = (qd & 1) * 32 + T;      // index among the owner's 64 queries
+              if (static_cast<uint32_t>(qd >> 1) == rank) fc2_mine[slot] = tot;
+              else st_cluster_f32(map_to_cta(smem_u32(fc2_peer + slot), peer), tot);
             }
-            epi_bar_sync();
+            pair_epi_bar_sync();
           }
           tc_fence_before();
           // hand-over of the partial sums, then the owner finishes its 64 queries
-          if (e == 0) {
+          if (T == 0) {
             mbar_arrive_remote(map_to_cta(bar_fc2, peer));
             *epi_ok = mbar_wait_cluster(bar_fc2, tile_no & 1u, abort_flag, p.status, 0x312) ? 1 : 0;
           }
-          epi_bar_sync();
+          pair_epi_bar_sync();
           if (*epi_ok == 0) { ok = false; break; }
-          if (e < kPairHalfQ) {
-            const int64_t q = q0 + e;
-            if (q < p.Q) p.out[q] = fc2_mine[e] + fc2_peer[e] + p.fc2_b;
+          if (T < kPairHalfQ) {
+            const int64_t q = q0 + T;
+            if (q < p.Q) p.out[q] = fc2_mine[T] + fc2_peer[T] + p.fc2_b;
           }
-          epi_bar_sync();
+          pair_epi_bar_sync();
           if (timed) { c_wait += c1 - c0; c_fc2 += clock64() - c1; ++c_layers; }
         }
       }
@@ -906,13 +977,14 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
     if (timed) {
       p.phase_cycles[0] = c_wait; p.phase_cycles[1] = c_epi;
       p.phase_cycles[2] = c_fc2; p.phase_cycles[3] = c_layers;
+      p.phase_cycles[12] = c_ld; p.phase_cycles[13] = c_bias; p.phase_cycles[14] = c_sync; p.phase_cycles[15] = c_rem; p.phase_cycles[11] = c_loc;
     }
   }
 
   // ------------------------------ teardown ------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp >= 6 && lane == 0 && *abort_flag && warp - 6 < kPairStages && issued > 0) {
+  if (warp >= 6 && warp < 12 && lane == 0 && *abort_flag && warp - 6 < kPairStages && issued > 0) {
     const uint32_t j = issued - 1;
     const uint32_t ph = (j / kPairStages) & 1u;
     const long long t0 = clock64();
@@ -1099,7 +1171,7 @@ extern "C" hb_status hb_mlp_predict(hb_mlp* h, const float* op_features, const u
   } else {
     // one cluster of two CTAs per tile of 128 queries, at most one cluster per SM pair
     const int pairs = static_cast<int>(tiles < h->sm_count / 2 ? tiles : h->sm_count / 2);
-    mlp_chain_pair_kernel<<<2 * pairs, kThreads, kPairSmemBytes, s>>>(p);
+    mlp_chain_pair_kernel<<<2 * pairs, kPairThreads, kPairSmemBytes, s>>>(p);
   }
   HB_CUDA_TRY(cudaGetLastError());
   return HB_OK;
