@@ -336,7 +336,7 @@ def main():
                            "launch": "the timed steps are replayed from one CUDA graph; a step is the "
                                      "wave-scale kernel plus the per-destination totals",
                            "collective": "one all-reduce of the [steps x 6] totals" if world > 1 else "none"},
-                "roofline": {"bound": "hbm", "kernel": "wave_scale_fast_kernel<4,false>",
+                "roofline": {"bound": "hbm", "kernel": "wave_scale_class_kernel<2>",
                              "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                              "us_per_launch": kern_ms * 1e3,

@@ -243,46 +243,75 @@ struct FastKernel {   // per recorded kernel, device independent
   uint32_t m_wpb;
 };
 
-HB_HD int32_t fast_occupancy(const FastDev& d, const FastKernel& k,
-                                                  int32_t regs, int32_t rpw_units, uint32_t m_rpw,
-                                                  const uint32_t* __restrict__ s_magic) {
-  if (k.block_size <= 0 || k.block_size > d.max_threads_per_block || regs > 256 || k.smem < 0)
-    return 0;
-  // registers: allocation unit 256 per warp, checked against the per-block file
-  // with the warp count rounded up to the number of sub-partitions
-  int32_t lr = HB_INT_MAX;
-  if (rpw_units > 0) {
-    const int32_t pm = (1 << d.parts_shift) - 1;
-    const int32_t wpb_up = (k.wpb + pm) & ~pm;
-    if (d.regs_per_block < ((rpw_units * wpb_up) << 8)) return 0;
-    const uint32_t warps_part = udiv_magic(d.regs_units, rpw_units, m_rpw);
-    lr = udiv_magic(warps_part << d.parts_shift, k.wpb, k.m_wpb);
-    if (d.gp100_units4 >= 0 && lr != 0) {
-      if (d.regs_per_block < ((rpw_units * ((k.wpb + 3) & ~3)) << 8) ||
-          udiv_magic(udiv_magic(d.gp100_units4, rpw_units, m_rpw) << 2, k.wpb, k.m_wpb) == 0)
-        return 0;
-    }
+// The three device-dependent limits, each reading only "its" fields of the row,
+// so that rows which agree on those fields can share one evaluation.
+// Registers: allocation unit 256 per warp, checked against the per-block file
+// with the warp count rounded up to the number of sub-partitions.
+HB_HD int32_t fast_regs_limit(const FastDev& d, const FastKernel& k, int32_t regs,
+                              int32_t rpw_units, uint32_t m_rpw) {
+  if (regs > 256) return 0;
+  if (rpw_units <= 0) return HB_INT_MAX;
+  const int32_t pm = (1 << d.parts_shift) - 1;
+  const int32_t wpb_up = (k.wpb + pm) & ~pm;
+  if (d.regs_per_block < ((rpw_units * wpb_up) << 8)) return 0;
+  const uint32_t warps_part = udiv_magic(d.regs_units, rpw_units, m_rpw);
+  int32_t lr = static_cast<int32_t>(udiv_magic(warps_part << d.parts_shift, k.wpb, k.m_wpb));
+  if (d.gp100_units4 >= 0 && lr != 0) {
+    if (d.regs_per_block < ((rpw_units * ((k.wpb + 3) & ~3)) << 8) ||
+        udiv_magic(udiv_magic(d.gp100_units4, rpw_units, m_rpw) << 2, k.wpb, k.m_wpb) == 0)
+      lr = 0;
   }
-  const int32_t lw = udiv_magic(d.max_warps, k.wpb, k.m_wpb);
-  // shared memory
+  return lr;
+}
+
+HB_HD int32_t fast_warps_limit(const FastDev& d, const FastKernel& k) {
+  if (k.block_size <= 0 || k.block_size > d.max_threads_per_block) return 0;
+  return static_cast<int32_t>(udiv_magic(d.max_warps, k.wpb, k.m_wpb));
+}
+
+// 0 also stands for "the calculator reports an error" (occupancy 0 either way).
+HB_HD int32_t fast_smem_limit(const FastDev& d, const FastKernel& k,
+                              const uint32_t* __restrict__ s_magic) {
+  if (k.smem < 0) return 0;
   const int32_t units = (k.smem + d.smem_reserved + (1 << d.gran_shift) - 1) >> d.gran_shift;
   const int32_t alloc = units << d.gran_shift;
   if (alloc > d.smem_cap) return 0;
-  int32_t ls = HB_INT_MAX;
-  if (units > 0) {
-    int32_t budget = d.smem_pref;
-    if (budget < alloc) {
-      budget = d.ladder_kind == 0 ? d.smem_per_sm : hb_carveout_snap(d.ladder_kind, d.smem_per_sm, alloc);
-      if (budget < 0) return 0;
-    }
-    ls = units < kMagicN ? udiv_magic(budget >> d.gran_shift, units, s_magic[units])
-                         : (budget >> d.gran_shift) / units;
+  if (units <= 0) return HB_INT_MAX;
+  int32_t budget = d.smem_pref;
+  if (budget < alloc) {
+    budget = d.ladder_kind == 0 ? d.smem_per_sm : hb_carveout_snap(d.ladder_kind, d.smem_per_sm, alloc);
+    if (budget < 0) return 0;
   }
+  return units < kMagicN
+             ? static_cast<int32_t>(udiv_magic(budget >> d.gran_shift, units, s_magic[units]))
+             : (budget >> d.gran_shift) / units;
+}
+
+HB_HD int32_t fast_occupancy(const FastDev& d, const FastKernel& k, int32_t regs, int32_t rpw_units,
+                             uint32_t m_rpw, const uint32_t* __restrict__ s_magic) {
+  // an invalid block size zeroes the warp limit, hence the result
+  const int32_t lw = fast_warps_limit(d, k);
+  if (lw == 0) return 0;
+  const int32_t lr = fast_regs_limit(d, k, regs, rpw_units, m_rpw);
+  const int32_t ls = fast_smem_limit(d, k, s_magic);
   int32_t occ = lr < ls ? lr : ls;
   occ = occ < lw ? occ : lw;
   return occ < d.blocks_limit ? occ : d.blocks_limit;
 }
 
+// Rows that agree on the fields one limit reads form a class for that limit.
+inline bool same_regs_class(const FastDev& a, const FastDev& b) {
+  return a.regs_per_block == b.regs_per_block && a.regs_units == b.regs_units &&
+         a.parts_shift == b.parts_shift && a.gp100_units4 == b.gp100_units4;
+}
+inline bool same_warps_class(const FastDev& a, const FastDev& b) {
+  return a.max_warps == b.max_warps && a.max_threads_per_block == b.max_threads_per_block;
+}
+inline bool same_smem_class(const FastDev& a, const FastDev& b) {
+  return a.gran_shift == b.gran_shift && a.smem_reserved == b.smem_reserved &&
+         a.smem_cap == b.smem_cap && a.smem_pref == b.smem_pref && a.ladder_kind == b.ladder_kind &&
+         a.smem_per_sm == b.smem_per_sm;
+}
 
 // Whether a device row fits the fast path's assumptions.
 inline bool fast_row_ok(const hb_device_spec& s, const hb_dev_pre& pre) {

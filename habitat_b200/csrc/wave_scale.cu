@@ -14,6 +14,7 @@
 // The kernel is HBM-bound by design: 20 B read + 5 B written per kernel and
 // 9 B written per pair.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -346,6 +347,182 @@ bool vec4_ok(const Ptrs& p, int64_t K, bool need_gamma) {
          (!p.dest_regs || reinterpret_cast<uintptr_t>(p.dest_regs) % 8 == 0);
 }
 
+// ---------------------------------------------------------------------------
+// Class kernel.  Device rows usually differ in only a few of the fields the
+// occupancy rules read (all six benchmark rows share one register file shape,
+// two warp budgets and three shared-memory budgets).  The host groups the rows
+// of a launch into classes per limit; a thread evaluates each class once per
+// kernel record and a destination only picks its three limits and takes the
+// minimum.  Up to four classes per limit, no per-destination register
+// overrides; anything else takes wave_scale_fast_kernel.
+// ---------------------------------------------------------------------------
+constexpr int kMaxClasses = 4;
+
+struct ClassDev {
+  int32_t num_sms;
+  uint32_t sms_magic;
+  float a_hi, a_lo, b_hi, b_lo;
+  float clk_hi, clk_lo;     // log2 of the clock ratio, split
+  uint8_t rc, wc, sc, blocks_limit;
+};
+
+struct ClassParams {
+  int32_t D, n_rc, n_wc, n_sc;
+  int64_t K;
+  FastDev cls_r[kMaxClasses], cls_w[kMaxClasses], cls_s[kMaxClasses];
+  ClassDev origin;
+  ClassDev dest[HB_MAX_DEVICES / 2];
+};
+
+__device__ __forceinline__ int32_t pick4(const int32_t (&v)[kMaxClasses], uint32_t c) {
+  return c == 0 ? v[0] : (c == 1 ? v[1] : (c == 2 ? v[2] : v[3]));
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(128)
+wave_scale_class_kernel(const Ptrs p, const __grid_constant__ ClassParams cp) {
+  __shared__ uint32_t s_magic[kMagicN];
+  __shared__ uint32_t s_wave_magic[HB_MAX_DEVICES / 2 + 1][33];
+  __shared__ float2 s_log2[33];   // log2(i) as float hi + lo
+  for (int i = threadIdx.x; i < kMagicN; i += blockDim.x) s_magic[i] = g_magic[i];
+  for (int i = threadIdx.x; i < (cp.D + 1) * 33; i += blockDim.x) {
+    const int d = i / 33, occ = i - d * 33;
+    const uint32_t wave = static_cast<uint32_t>((d == 0 ? cp.origin.num_sms : cp.dest[d - 1].num_sms) * occ);
+    s_wave_magic[d][occ] = wave >= 2u ? 0xFFFFFFFFu / wave + ((0xFFFFFFFFu % wave) + 1u == wave ? 1u : 0u) + 1u : 0u;
+  }
+  if (threadIdx.x < 33) {
+    const double l = c_log2_int[threadIdx.x];
+    const float hi = static_cast<float>(l);
+    s_log2[threadIdx.x] = make_float2(hi, static_cast<float>(l - static_cast<double>(hi)));
+  }
+  __syncthreads();
+
+  const int64_t K = cp.K;
+  const int64_t k0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
+  if (k0 >= K) return;
+
+  const Vec<int32_t, VEC> nbv = load_vec<int32_t, VEC>(p.num_blocks + k0);
+  const Vec<uint16_t, VEC> bsv = load_vec<uint16_t, VEC>(p.block_size + k0);
+  const Vec<uint16_t, VEC> rgv = load_vec<uint16_t, VEC>(p.regs + k0);
+  const Vec<uint32_t, VEC> smv = load_vec<uint32_t, VEC>(p.smem + k0);
+  const Vec<float, VEC> tv = load_vec<float, VEC>(p.time_ns + k0);
+  const Vec<float, VEC> gv = load_vec<float, VEC>(p.gamma + k0);
+
+  int32_t lr[VEC][kMaxClasses], lw[VEC][kMaxClasses], ls[VEC][kMaxClasses];
+  int32_t wave_o[VEC];
+  float2 lg_o[VEC];   // log2 of the origin's per-SM block count (small-kernel branch)
+  Vec<uint8_t, VEC> oocc;
+  Vec<uint32_t, VEC> owav;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    FastKernel k;
+    k.block_size = bsv.v[i];
+    k.wpb = (k.block_size + 31) >> 5;
+    k.regs = rgv.v[i];
+    k.rpw_units = (k.regs + 7) >> 3;
+    k.smem = smv.v[i] > 0x7FFF0000u ? -1 : static_cast<int32_t>(smv.v[i]);
+    k.m_wpb = s_magic[min(k.wpb, kMagicN - 1)];
+    const uint32_t m_rpw = s_magic[min(k.rpw_units, kMagicN - 1)];
+#pragma unroll
+    for (int c = 0; c < kMaxClasses; ++c) {
+      lr[i][c] = c < cp.n_rc ? fast_regs_limit(cp.cls_r[c], k, k.regs, k.rpw_units, m_rpw) : 0;
+      lw[i][c] = c < cp.n_wc ? fast_warps_limit(cp.cls_w[c], k) : 0;
+      ls[i][c] = c < cp.n_sc ? fast_smem_limit(cp.cls_s[c], k, s_magic) : 0;
+    }
+    const int32_t occ = min(min(pick4(lr[i], cp.origin.rc), pick4(ls[i], cp.origin.sc)),
+                            min(pick4(lw[i], cp.origin.wc), static_cast<int32_t>(cp.origin.blocks_limit)));
+    const int32_t nb = nbv.v[i];
+    wave_o[i] = cp.origin.num_sms * occ;
+    oocc.v[i] = static_cast<uint8_t>(occ);
+    owav.v[i] = (occ > 0 && nb >= 1)
+                    ? udiv_magic_fix(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_o[i]),
+                                     s_wave_magic[0][occ])
+                    : 0xFFFFFFFFu;
+    // ceil(nb / num_sms) <= occupancy <= 32 whenever the small-kernel branch is taken
+    const uint32_t om = (nb >= 1 && nb < wave_o[i])
+                            ? udiv_magic(nb + cp.origin.num_sms - 1, cp.origin.num_sms, cp.origin.sms_magic)
+                            : 1u;
+    lg_o[i] = s_log2[om];
+  }
+  store_vec<uint8_t, VEC>(p.origin_occ + k0, oocc);
+  store_vec<uint32_t, VEC>(p.origin_waves + k0, owav);
+
+  for (int d = 0; d < cp.D; ++d) {
+    const ClassDev& dd = cp.dest[d];
+    const int64_t base = static_cast<int64_t>(d) * K + k0;
+    const uint32_t rc = dd.rc, wc = dd.wc, sc = dd.sc;
+    const int32_t bl = dd.blocks_limit;
+    Vec<float, VEC> outv;
+    Vec<uint8_t, VEC> occv;
+    Vec<uint32_t, VEC> wavv;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int32_t nb = nbv.v[i];
+      const int32_t occ = min(min(pick4(lr[i], rc), pick4(ls[i], sc)), min(pick4(lw[i], wc), bl));
+      const int32_t wave_d = dd.num_sms * occ;
+      occv.v[i] = static_cast<uint8_t>(occ);
+      wavv.v[i] = (occ > 0 && nb >= 1)
+                      ? udiv_magic_fix(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_d),
+                                       s_wave_magic[d + 1][occ])
+                      : 0xFFFFFFFFu;
+      const float gamma = gv.v[i];
+      const bool live = nb >= 1 && wave_o[i] != 0;
+      const bool small = live && nb < wave_o[i] && nb < wave_d;
+      const bool ok = live && !(nb < wave_o[i] && wave_d == 0);
+      // small kernel (roofline.py:32-45): exponent (1 - gamma) (log2 clk + log2 dmax - log2 omax),
+      // both per-SM block counts <= 32; log2 values carried as float hi + lo
+      const uint32_t dm = small ? udiv_magic(nb + dd.num_sms - 1, dd.num_sms, dd.sms_magic) : 1u;
+      const float2 lg_d = s_log2[dm];
+      const float e_small = (1.0f - gamma) * ((lg_d.x - lg_o[i].x) + ((lg_d.y - lg_o[i].y) + dd.clk_lo) + dd.clk_hi);
+      const float e_large = fmaf(gamma, dd.a_hi, dd.b_hi) + fmaf(gamma, dd.a_lo, dd.b_lo);
+      const float e = small ? e_small : e_large;
+      outv.v[i] = ok ? tv.v[i] * ex2_approx(e) : __int_as_float(0x7FC00000);
+    }
+    store_vec<float, VEC>(p.scaled_ns + base, outv);
+    store_vec<uint8_t, VEC>(p.dest_occ + base, occv);
+    store_vec<uint32_t, VEC>(p.dest_waves + base, wavv);
+  }
+}
+
+// Finds (or appends) the class of `f` under `same`; returns -1 when full.
+template <typename Same>
+int class_of(FastDev* classes, int32_t* n, const FastDev& f, Same same) {
+  for (int c = 0; c < *n; ++c)
+    if (same(classes[c], f)) return c;
+  if (*n >= kMaxClasses) return -1;
+  classes[*n] = f;
+  return (*n)++;
+}
+
+bool build_class_params(const FastParams& fp, ClassParams* cp) {
+  std::memset(cp, 0, sizeof(*cp));
+  cp->D = fp.D;
+  cp->K = fp.K;
+  for (int d = -1; d < fp.D; ++d) {
+    const FastDev& f = d < 0 ? fp.origin : fp.dest[d];
+    ClassDev& c = d < 0 ? cp->origin : cp->dest[d];
+    const int rc = class_of(cp->cls_r, &cp->n_rc, f, same_regs_class);
+    const int wc = class_of(cp->cls_w, &cp->n_wc, f, same_warps_class);
+    const int sc = class_of(cp->cls_s, &cp->n_sc, f, same_smem_class);
+    if (rc < 0 || wc < 0 || sc < 0 || f.blocks_limit > 255) return false;
+    c.rc = static_cast<uint8_t>(rc);
+    c.wc = static_cast<uint8_t>(wc);
+    c.sc = static_cast<uint8_t>(sc);
+    c.blocks_limit = static_cast<uint8_t>(f.blocks_limit);
+    c.num_sms = f.num_sms;
+    c.sms_magic = f.sms_magic;
+    c.a_hi = f.a_hi; c.a_lo = f.a_lo; c.b_hi = f.b_hi; c.b_lo = f.b_lo;
+    c.clk_hi = static_cast<float>(f.log2_clk);
+    c.clk_lo = static_cast<float>(f.log2_clk - static_cast<double>(c.clk_hi));
+  }
+  return true;
+}
+
 // Fast path when every row of the launch qualifies and only the five standard
 // outputs are wanted; returns false (nothing launched) otherwise.
 bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream, hb_status* st) {
@@ -374,6 +551,22 @@ bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream,
     hb::set_error("hb_wave_scale: K too large for one launch");
     *st = HB_ERR_TOO_LARGE;
     return true;
+  }
+  ClassParams cp;
+  if (!p.dest_regs && build_class_params(fp, &cp)) {
+    const int cthreads = 128;
+    static const int vec_pref = [] { const char* e = std::getenv("HB_WAVE_VEC"); return e ? std::atoi(e) : 2; }();
+    // two records per thread measured fastest (more resident warps than four per thread)
+    const int cvec = vec4 ? (vec_pref == 4 ? 4 : (vec_pref == 1 ? 1 : 2)) : 1;
+    const int64_t cblocks = ((K + cvec - 1) / cvec + cthreads - 1) / cthreads;
+    if (cblocks <= 0x7FFFFFFF) {
+      if (cvec == 4) wave_scale_class_kernel<4><<<static_cast<unsigned>(cblocks), cthreads, 0, stream>>>(p, cp);
+      else if (cvec == 2) wave_scale_class_kernel<2><<<static_cast<unsigned>(cblocks), cthreads, 0, stream>>>(p, cp);
+      else wave_scale_class_kernel<1><<<static_cast<unsigned>(cblocks), cthreads, 0, stream>>>(p, cp);
+      const cudaError_t ce = cudaGetLastError();
+      *st = ce == cudaSuccess ? HB_OK : hb::cuda_fail(ce, "wave_scale_class_kernel launch");
+      return true;
+    }
   }
   const dim3 grid(static_cast<unsigned>(blocks));
   if (vec4) {
