@@ -374,8 +374,9 @@ struct ClassParams {
   ClassDev dest[HB_MAX_DEVICES / 2];
 };
 
-__device__ __forceinline__ int32_t pick4(const int32_t (&v)[kMaxClasses], uint32_t c) {
-  return c == 0 ? v[0] : (c == 1 ? v[1] : (c == 2 ? v[2] : v[3]));
+// Byte c of a packed word (one permute instruction).
+__device__ __forceinline__ int32_t pick_byte(uint32_t packed, uint32_t c) {
+  return static_cast<int32_t>(__byte_perm(packed, 0u, 0x4440u | c));
 }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -413,7 +414,9 @@ wave_scale_class_kernel(const Ptrs p, const __grid_constant__ ClassParams cp) {
   const Vec<float, VEC> tv = load_vec<float, VEC>(p.time_ns + k0);
   const Vec<float, VEC> gv = load_vec<float, VEC>(p.gamma + k0);
 
-  int32_t lr[VEC][kMaxClasses], lw[VEC][kMaxClasses], ls[VEC][kMaxClasses];
+  // the class limits of a record, one byte each (values above 255 cannot win the
+  // minimum against the blocks-per-SM limit, which is at most 32)
+  uint32_t lr[VEC], lw[VEC], ls[VEC];
   int32_t wave_o[VEC];
   float2 lg_o[VEC];   // log2 of the origin's per-SM block count (small-kernel branch)
   Vec<uint8_t, VEC> oocc;
@@ -428,14 +431,15 @@ wave_scale_class_kernel(const Ptrs p, const __grid_constant__ ClassParams cp) {
     k.smem = smv.v[i] > 0x7FFF0000u ? -1 : static_cast<int32_t>(smv.v[i]);
     k.m_wpb = s_magic[min(k.wpb, kMagicN - 1)];
     const uint32_t m_rpw = s_magic[min(k.rpw_units, kMagicN - 1)];
+    lr[i] = lw[i] = ls[i] = 0;
 #pragma unroll
     for (int c = 0; c < kMaxClasses; ++c) {
-      lr[i][c] = c < cp.n_rc ? fast_regs_limit(cp.cls_r[c], k, k.regs, k.rpw_units, m_rpw) : 0;
-      lw[i][c] = c < cp.n_wc ? fast_warps_limit(cp.cls_w[c], k) : 0;
-      ls[i][c] = c < cp.n_sc ? fast_smem_limit(cp.cls_s[c], k, s_magic) : 0;
+      if (c < cp.n_rc) lr[i] |= static_cast<uint32_t>(min(fast_regs_limit(cp.cls_r[c], k, k.regs, k.rpw_units, m_rpw), 255)) << (8 * c);
+      if (c < cp.n_wc) lw[i] |= static_cast<uint32_t>(min(fast_warps_limit(cp.cls_w[c], k), 255)) << (8 * c);
+      if (c < cp.n_sc) ls[i] |= static_cast<uint32_t>(min(fast_smem_limit(cp.cls_s[c], k, s_magic), 255)) << (8 * c);
     }
-    const int32_t occ = min(min(pick4(lr[i], cp.origin.rc), pick4(ls[i], cp.origin.sc)),
-                            min(pick4(lw[i], cp.origin.wc), static_cast<int32_t>(cp.origin.blocks_limit)));
+    const int32_t occ = min(min(pick_byte(lr[i], cp.origin.rc), pick_byte(ls[i], cp.origin.sc)),
+                            min(pick_byte(lw[i], cp.origin.wc), static_cast<int32_t>(cp.origin.blocks_limit)));
     const int32_t nb = nbv.v[i];
     wave_o[i] = cp.origin.num_sms * occ;
     oocc.v[i] = static_cast<uint8_t>(occ);
@@ -463,7 +467,7 @@ wave_scale_class_kernel(const Ptrs p, const __grid_constant__ ClassParams cp) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int32_t nb = nbv.v[i];
-      const int32_t occ = min(min(pick4(lr[i], rc), pick4(ls[i], sc)), min(pick4(lw[i], wc), bl));
+      const int32_t occ = min(min(pick_byte(lr[i], rc), pick_byte(ls[i], sc)), min(pick_byte(lw[i], wc), bl));
       const int32_t wave_d = dd.num_sms * occ;
       occv.v[i] = static_cast<uint8_t>(occ);
       wavv.v[i] = (occ > 0 && nb >= 1)
