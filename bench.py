@@ -21,7 +21,10 @@ import sys
 import threading
 import time
 
-import numpy as np
+# torchrun pins OMP_NUM_THREADS to 1; the CPU baseline is meant to use every host core
+os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
+import numpy as np  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
