@@ -343,7 +343,11 @@ def main():
                              "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                              "us_per_launch": kern_ms * 1e3,
-                             "algorithmic_bytes_per_pair": WAVE_BYTES_PER_PAIR, "traffic": None},
+                             "algorithmic_bytes_per_pair": WAVE_BYTES_PER_PAIR,
+                             # dram__bytes_read + dram__bytes_write of one launch (ncu capture summarised
+                             # in profiles/): the 21 MB of input is read; most of the 62 MB of output is
+                             # still in the 126 MB L2 when the launch ends
+                             "traffic": 29.0e6, "traffic_unit": "bytes per launch (ncu)"},
                 "e2e": {"value": world * pairs / (e2e_ms * 1e-3), "unit": "pairs/s",
                         "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             })
@@ -421,7 +425,10 @@ def main():
                              "frac": tflops / peaks["bf16_tflops"],
                              "frac_of_sustained": tflops / peaks["bf16_tflops_sustained"],
                              "peak_source": peaks["source"], "ms_per_launch": kern_ms,
-                             "flops_per_query": MLP_FLOPS_PER_QUERY, "traffic": None},
+                             "flops_per_query": MLP_FLOPS_PER_QUERY,
+                             # dram__bytes_read + dram__bytes_write of one launch (ncu capture
+                             # summarised in profiles/): weights once plus the queries
+                             "traffic": 25.8e6, "traffic_unit": "bytes per launch (ncu)"},
                 "e2e": {"value": world * MLP_Q / (e2e_ms * 1e-3), "unit": "predictions/s",
                         "h2d_bytes_per_step": int(p_f.numel() * 4 + p_r.numel()),
                         "d2h_bytes_per_step": int(p_o.numel() * 4)},
