@@ -1,0 +1,62 @@
+"""Host pipelines (pinned memory in and out, two streams) against the device entry points."""
+import numpy as np
+import pytest
+import torch
+
+from habitat_b200 import batched, hostio, workloads
+from tests.helpers import run_wave_oracle, to_numpy
+
+pytestmark = pytest.mark.gpu
+
+
+def _pinned(arrays):
+    out = {}
+    for k, v in arrays.items():
+        a = np.ascontiguousarray(v.astype(np.float32) if k == "run_time_ns" else v)
+        if a.dtype == np.uint16:
+            a = a.view(np.int16)
+        elif a.dtype == np.uint32:
+            a = a.view(np.int32)
+        out[k] = torch.from_numpy(a).pin_memory()
+    return out
+
+
+def test_wave_scale_pipeline(bench_devices):
+    K = 40000
+    batches = [workloads.make_kernels(K, seed=300 + i) for i in range(5)]
+    pipe = hostio.WaveScaleHost(bench_devices[0], bench_devices, K, depth=2)
+    for i, b in enumerate(batches):
+        slot = i % 2
+        pipe.wait(slot)                      # results of batch i - 2 were consumed below
+        pipe.submit(_pinned(b), slot)
+        if i >= 1:                           # check the previous batch while this one runs
+            prev = (i - 1) % 2
+            pipe.wait(prev)
+            ref = run_wave_oracle(batches[i - 1], bench_devices[0], bench_devices)
+            got = {k: to_numpy(v) for k, v in pipe.host_out[prev].items()}
+            for key in ("dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves"):
+                assert np.array_equal(got[key], ref[key])
+            ok = ref["status"] <= 1
+            assert np.isnan(got["scaled_ns"][~ok]).all()
+            err = np.abs(got["scaled_ns"][ok] - ref["scaled_ns"][ok]) / ref["scaled_ns"][ok]
+            assert err.max() <= 1e-6
+    assert pipe.h2d_bytes == 20 * K and pipe.d2h_bytes == (9 * 6 + 5) * K
+
+
+def test_mlp_pipeline():
+    op, Q = "linear", 5000
+    w = workloads.torch_init_mlp_weights(op)
+    feats, dev = workloads.make_queries(op, Q, 17)
+    mu, sigma = workloads.batch_mu_sigma(feats, dev)
+    h = batched.MLPHandle(4, mu=mu, sigma=sigma, device_features=workloads.BENCH_DEVICE_FEATURES, **w)
+    want = h.predict(torch.from_numpy(feats).cuda(), torch.from_numpy(dev).cuda()).cpu()
+    pipe = hostio.MLPPredictHost(h, Q, depth=2)
+    pf, pr = torch.from_numpy(feats).pin_memory(), torch.from_numpy(dev).pin_memory()
+    for i in range(4):
+        pipe.wait(i % 2)
+        pipe.submit(pf, pr, i % 2)
+    for slot in range(2):
+        pipe.wait(slot)
+        assert torch.equal(pipe.host_out[slot], want)
+    h.check_status()
+    h.close()
