@@ -551,11 +551,12 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
 constexpr int kPairQ = 128;                 // queries per cluster tile
 constexpr int kPairHalfQ = 64;              // activation rows resident per CTA
 constexpr int kPairMT = kWidth / 256;       // 4 MMA row blocks per layer
-constexpr int kPairStages = 6;
+constexpr int kPairStages = 3;               // ring slots, each two weight tiles (two K blocks)
+constexpr int kPairStageBytes = 2 * kTileBytes;
 constexpr int kPairActKb = kPairHalfQ * 128;          // 8 KB per K block
 constexpr int kPairActBytes = kNumKB * kPairActKb;    // 128 KB
 constexpr int kPairThreads = 512;              // warps: 0 alloc, 1 MMA, 2-5 + 12-15 epilogue, 6-11 producers
-constexpr int kPairSmemBytes = kPairActBytes + kPairStages * kTileBytes + 1024 + 1024;
+constexpr int kPairSmemBytes = kPairActBytes + kPairStages * kPairStageBytes + 1024 + 1024;
 static_assert(kPairSmemBytes <= 232448, "over the 227 KB shared-memory limit");
 
 __device__ __forceinline__ void pair_epi_bar_sync() {
@@ -658,7 +659,7 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
 
   const uint32_t act = base;
   const uint32_t stage0 = base + kPairActBytes;
-  const uint32_t bars = stage0 + kPairStages * kTileBytes;
+  const uint32_t bars = stage0 + kPairStages * kPairStageBytes;
   uint8_t* bars_ptr = base_ptr + (bars - base);
   // barrier block (same offsets in both CTAs)
   const uint32_t bar_full = bars;                          // [stages] weight halves landed (leader: both CTAs')
@@ -727,16 +728,19 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
         size_t layer_base = 0;   // in tile images
         for (int L = 0; L < n_layers && ok; ++L) {
           const int nkb = L == 0 ? 1 : kNumKB;
+          // a ring slot takes two consecutive K blocks of one output block (fc1 has only one)
+          const int n_loads = (nkb + 1) / 2;
+          const uint32_t load_bytes = nkb == 1 ? kTileBytes : kPairStageBytes;
           for (int j = 0; j < kPairMT && ok; ++j) {
             const size_t blk = layer_base + static_cast<size_t>(2 * j + rank) * nkb;
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
+            for (int g = 0; g < n_loads; ++g, ++it) {
               if (it % kPairStages != w) continue;
               const uint32_t ph = (it / kPairStages) & 1u;
               const long long q0 = ptimed ? clock64() : 0;
               if (!mbar_wait(bar_empty + 8 * w, ph ^ 1u, abort_flag, p.status, 0x111)) { ok = false; break; }
               const long long q1 = ptimed ? clock64() : 0;
-              mbar_expect_tx(bar_full + 8 * w, kTileBytes);
-              bulk_g2s(stage0 + w * kTileBytes, p.wpack + (blk + kb) * kTileBytes, kTileBytes,
+              mbar_expect_tx(bar_full + 8 * w, load_bytes);
+              bulk_g2s(stage0 + w * kPairStageBytes, p.wpack + (blk + 2 * g) * kTileBytes, load_bytes,
                        bar_full + 8 * w);
               issued = it + 1;
               if (rank == 1) {
@@ -779,19 +783,27 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
           const int nkb = L == 0 ? 1 : kNumKB;
           for (int j = 0; j < kPairMT && ok; ++j) {
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(j * kPairQ);
-            for (int kb = 0; kb < nkb; ++kb) {
+            for (int g = 0; g < (nkb + 1) / 2; ++g) {
               const long long m1 = mtimed ? clock64() : 0;
               if (!mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, 0x212)) { ok = false; break; }
               const long long m2 = mtimed ? clock64() : 0;
               const long long m3 = m2;
               tc_fence_after();
-              const uint64_t a0 = desc_hi | (a_lo0 + s * (kTileBytes >> 4));
-              const uint64_t b0 = desc_hi | (b_lo0 + static_cast<uint32_t>(kb) * (kPairActKb >> 4));
+              const uint64_t a0 = desc_hi | (a_lo0 + s * (kPairStageBytes >> 4));
+              const uint64_t b0 = desc_hi | (b_lo0 + static_cast<uint32_t>(2 * g) * (kPairActKb >> 4));
               // a K step of 16: 32 bytes along an A row, 16 K rows (2 KB) of B
-              tc_mma_pair_bf16(d_tmem, a0, b0, idesc, kb != 0 ? 1u : 0u);
+              tc_mma_pair_bf16(d_tmem, a0, b0, idesc, g != 0 ? 1u : 0u);
               tc_mma_pair_bf16(d_tmem, a0 + 2, b0 + 128, idesc, 1u);
               tc_mma_pair_bf16(d_tmem, a0 + 4, b0 + 256, idesc, 1u);
               tc_mma_pair_bf16(d_tmem, a0 + 6, b0 + 384, idesc, 1u);
+              if (nkb > 1) {
+                // second K block of the slot: next weight tile (16 KB on), next 64 K rows (8 KB on)
+                const uint64_t a1 = a0 + (kTileBytes >> 4), b1 = b0 + (kPairActKb >> 4);
+                tc_mma_pair_bf16(d_tmem, a1, b1, idesc, 1u);
+                tc_mma_pair_bf16(d_tmem, a1 + 2, b1 + 128, idesc, 1u);
+                tc_mma_pair_bf16(d_tmem, a1 + 4, b1 + 256, idesc, 1u);
+                tc_mma_pair_bf16(d_tmem, a1 + 6, b1 + 384, idesc, 1u);
+              }
               tc_commit_pair(bar_empty + 8 * s);
               if (mtimed) { mc_full += m2 - m1; mc_peer += m3 - m2; mc_issue += clock64() - m3; ++mc_n; }
               if (++s == kPairStages) { s = 0; ph ^= 1u; }
