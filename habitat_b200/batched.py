@@ -237,12 +237,15 @@ class MLPHandle:
         _native.check(_native.load().hb_mlp_status(self._handle, ctypes.byref(code)))
 
     def phase_cycles(self):
-        """{wait, epilogue, fc2, layers} cycle counters of the last bf16 launch (synchronises)."""
+        """Cycle counters of the first cluster in the last bf16 launch (synchronises): epilogue group 0
+        (wait, epilogue, fc2, layers, epi_publish, epi_remote), the MMA issuer (mma_wait_act,
+        mma_wait_weights, mma_wait_tmem, mma_issue, slots; mma_total_cycles and mma_total_ns over the
+        same interval, whose ratio is the SM clock under load) and the first producer."""
         out = (ctypes.c_int64 * 16)()
         _native.check(_native.load().hb_mlp_phase_cycles(self._handle, out))
-        names = ("wait", "epilogue", "fc2", "layers", "mma_wait_act", "mma_wait_own", "mma_wait_peer",
-                 "mma_issue", "slots", "producer_wait_slot", "producer_copy", "copies", "epi_tmem_load",
-                 "epi_bias_load", "epi_publish", "epi_remote")
+        names = ("wait", "epilogue", "fc2", "layers", "mma_wait_act", "mma_wait_weights", "mma_wait_tmem",
+                 "mma_issue", "slots", "producer_wait_slot", "producer_copy", "copies", "mma_total_cycles",
+                 "mma_total_ns", "epi_publish", "epi_remote")
         return dict(zip(names, [int(x) for x in out]))
 
     def close(self):

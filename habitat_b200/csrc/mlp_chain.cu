@@ -16,7 +16,8 @@
 //                                     column block per 128-feature tile, so the
 //                                     whole layer output (1024 x TILE_Q) lives in
 //                                     TMEM until it is drained.
-// tcgen05.mma (kind::f16, bf16 inputs, fp32 accumulate) is issued by one thread;
+// tcgen05.mma (kind::f16, bf16 inputs, fp32 accumulate) is issued by one elected
+// lane of a warp that walks the issue loop as a whole;
 // the epilogue warps read TMEM with tcgen05.ld, add the bias, apply ReLU, round
 // to bf16 and overwrite the activation buffer in place - legal because the
 // complete layer output is parked in TMEM before the first write.  fc2 is a dot
@@ -35,9 +36,10 @@
 // warps 2-5 = epilogue (one TMEM lane quadrant each), warps 6-11 = weight
 // producers.  Bulk copies issued by one thread complete one after the other
 // (measured: about 750 cycles each whatever their size), so the ring's slots
-// are dealt round-robin to several issuing warps to keep copies in flight.  Every mbarrier wait is bounded: when a wait runs out the
-// kernel records a status word, all roles leave their loops, outstanding bulk
+// are dealt round-robin to several issuing warps to keep copies in flight.
+// Every mbarrier wait is bounded: when a wait runs out the kernel records a status word, all roles leave their loops, outstanding bulk
 // copies are waited for (bounded) and TMEM is released.
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include <cmath>
@@ -91,7 +93,11 @@ struct MlpParams {
   float* out;                // [Q]
   int32_t num_tiles;
   int32_t* status;           // device word: 0 ok, else (role << 8 | site)
-  long long* phase_cycles;   // [4] cluster 0, leader: cycles waiting for MMAs, in hidden epilogues, in fc2; layers
+  long long* phase_cycles;   // [16] cluster 0: cycle counters of the roles (diagnostic), or null
+  CUtensorMap tmap_slot;     // pair kernel: the pack as [rows][128 B], box of two tile images (32 KB)
+  CUtensorMap tmap_tile;     // same tensor, box of one tile image (16 KB, fc1)
+  uint64_t unit_order;       // pair kernel: the 16 (block, K quarter) units of a hidden layer, 4 bits each
+  uint32_t unit_gates;       // pair kernel: 4 bits per block j: the block whose completion frees K quarter j
 };
 
 // ---------------------------------------------------------------------------
@@ -149,6 +155,15 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, ui
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
+}
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred)::"memory");
+  return pred;
 }
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -333,7 +348,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------
-    if (lane == 0) {
+    // The whole warp walks the loop and an elected lane issues (operands of tcgen05.mma
+    // are uniform registers; a loop run by one lane of a diverged warp issues slower).
+    {
       constexpr uint32_t idesc = make_idesc(TILE_Q);
       uint32_t it = 0, lay = 0;
       bool ok = true;
@@ -348,25 +365,27 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
               const uint32_t s = it % C::kStages;
               const uint32_t ph = (it / C::kStages) & 1u;
               if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x202)) { ok = false; break; }
-              tc_fence_after();
               const uint32_t a_base = stage0 + s * C::kStageBytes;
               const uint32_t b_base = act_hi + kb * C::kActKbBytes;
+              if (elect_one()) {
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks) {
-                const uint64_t a_hi = smem_desc_k128(a_base + ks * 32);
-                const uint64_t b_hi = smem_desc_k128(b_base + ks * 32);
-                tc_mma_bf16(d_tmem, a_hi, b_hi, idesc, (kb | ks) != 0 ? 1u : 0u);
-                if (SPLIT && L > 0) {
-                  const uint64_t a_lo = smem_desc_k128(a_base + kTileBytes + ks * 32);
-                  const uint64_t b_lo = smem_desc_k128(act_lo + kb * C::kActKbBytes + ks * 32);
-                  tc_mma_bf16(d_tmem, a_hi, b_lo, idesc, 1u);
-                  tc_mma_bf16(d_tmem, a_lo, b_hi, idesc, 1u);
+                for (int ks = 0; ks < 4; ++ks) {
+                  const uint64_t a_hi = smem_desc_k128(a_base + ks * 32);
+                  const uint64_t b_hi = smem_desc_k128(b_base + ks * 32);
+                  tc_mma_bf16(d_tmem, a_hi, b_hi, idesc, (kb | ks) != 0 ? 1u : 0u);
+                  if (SPLIT && L > 0) {
+                    const uint64_t a_lo = smem_desc_k128(a_base + kTileBytes + ks * 32);
+                    const uint64_t b_lo = smem_desc_k128(act_lo + kb * C::kActKbBytes + ks * 32);
+                    tc_mma_bf16(d_tmem, a_hi, b_lo, idesc, 1u);
+                    tc_mma_bf16(d_tmem, a_lo, b_hi, idesc, 1u);
+                  }
                 }
+                tc_commit(bar_empty + 8 * s);  // frees the ring slot once these MMAs retire
+                if (mt == kNumMT - 1 && kb == nkb - 1) tc_commit(bar_acc);  // the whole layer sits in TMEM
               }
-              tc_commit(bar_empty + 8 * s);  // frees the ring slot once these MMAs retire
+              __syncwarp();
             }
           }
-          if (ok) tc_commit(bar_acc);  // the whole layer sits in TMEM
         }
       }
     }
@@ -533,17 +552,23 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
 //     queries 64 c .. 64 c + 63; its TMEM receives the D rows of its features
 //     for all 128 queries.  Each weight byte is fetched once per pair.
 //   * The leader CTA (rank 0) issues every MMA.  A ring slot is ready when the
-//     leader's own bulk copy and the peer's have landed; each producer of the
-//     peer forwards the completion of its copy with a remote mbarrier arrive
-//     (one forwarding thread for all slots was measured to cap the ring at one
-//     slot per ~1100 cycles).  tcgen05.commit
-//     multicasts "slot free" and "layer done" to both CTAs.
+//     leader's weight box and the peer's have landed: both are tiled TMA loads
+//     (cp.async.bulk.tensor with .cta_group::2, no multicast) whose bytes are
+//     counted on the leader's barrier, so no thread of the peer has to forward
+//     anything.  tcgen05.commit multicasts "slot free" and "output block j
+//     accumulated" to both CTAs.
 //   * The activations are the MN-major B operand here (one 128-byte row of 64
 //     queries per K index): an epilogue thread owns one feature = one K row
 //     and writes eight queries per 16-byte store.
 //   * The epilogue of CTA c holds features x all 128 queries, but the next
 //     layer needs, in each CTA, all features x its 64 queries: half of the
-//     bf16 results are stored into the peer's shared memory (st.shared::cluster).
+//     bf16 results are stored into the peer's shared memory (st.async, counted
+//     in bytes on a barrier of the peer).
+//   * Epilogue and tensor core overlap: a hidden layer is issued as 16 units
+//     (output block, K quarter) in the order kPairOrder, so that output blocks
+//     finish one after the other and each frees the K quarter it will replace.
+//     The leader waits per K quarter (bar_actq) and per TMEM block (bar_tfree)
+//     instead of per layer; only the drain of the last block is exposed.
 //   * fc2: each CTA reduces its 512 features to 128 partial sums, hands the 64
 //     that belong to the peer's queries over through the peer's shared memory,
 //     and finishes its own 64 queries.
@@ -551,10 +576,23 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_con
 constexpr int kPairQ = 128;                 // queries per cluster tile
 constexpr int kPairHalfQ = 64;              // activation rows resident per CTA
 constexpr int kPairMT = kWidth / 256;       // 4 MMA row blocks per layer
-constexpr int kPairStages = 3;               // ring slots, each two weight tiles (two K blocks)
-constexpr int kPairStageBytes = 2 * kTileBytes;
+constexpr int kPairSlotKb = 2;               // weight tiles (K blocks of 64) per ring slot
+constexpr int kPairStages = 6 / kPairSlotKb; // ring slots: 96 KB in all
+constexpr int kPairStageBytes = kPairSlotKb * kTileBytes;
+static_assert(kPairStages <= 6, "one producer warp per ring slot, warps 6-11");
 constexpr int kPairActKb = kPairHalfQ * 128;          // 8 KB per K block
 constexpr int kPairActBytes = kNumKB * kPairActKb;    // 128 KB
+// Order of the 16 (output block j, K quarter q) units of a hidden layer, four bits each
+// (4 j + q), first unit in the low bits:
+//   (0,0) (1,0) (2,0) (3,0) | (0,1) (0,2) (0,3) | (1,1) (2,1) (3,1) | (1,2) (1,3) | (2,2) (3,2) | (2,3) | (3,3)
+// Block j completes after 7, 12, 15, 16 units, and by then no later unit reads quarter j,
+// so the epilogue of block j can replace quarter j of the activations in place while the
+// tensor core works on the remaining blocks; the next layer consumes the quarters in the
+// same order.
+constexpr uint64_t kPairOrder = 0xFBEA76D95321C840ull;
+constexpr uint32_t kPairGates = 0x3210u;
+__device__ __forceinline__ int pair_unit_j(uint64_t order, int u) { return static_cast<int>((order >> (4 * u + 2)) & 3u); }
+__device__ __forceinline__ int pair_unit_q(uint64_t order, int u) { return static_cast<int>((order >> (4 * u)) & 3u); }
 constexpr int kPairThreads = 512;              // warps: 0 alloc, 1 MMA, 2-5 + 12-15 epilogue, 6-11 producers
 constexpr int kPairSmemBytes = kPairActBytes + kPairStages * kPairStageBytes + 1024 + 1024;
 static_assert(kPairSmemBytes <= 232448, "over the 227 KB shared-memory limit");
@@ -575,12 +613,6 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                : "memory");
-}
-// Remote arrive without cluster-scope release: used to forward "my bulk copy
-// landed", where the data was written by the async proxy into this CTA's own
-// shared memory and is read there by this CTA's own tensor core.
-__device__ __forceinline__ void mbar_arrive_remote_plain(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -633,6 +665,23 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
                    : "memory");
 }
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Tiled TMA load of a box of 128-byte rows into this CTA's shared memory.  With
+// .cta_group::2 the completion may be counted on a barrier of the other CTA of the pair
+// (given as a shared::cluster address): both CTAs' weight copies report to the leader's
+// barrier directly.  No multicast: each CTA fetches its own half of the weights.
+__device__ __forceinline__ void tma_rows_2sm(uint32_t dst, const CUtensorMap* map, int32_t row,
+                                             uint32_t cluster_mbar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_mbar), "r"(0), "r"(row)
+      : "memory");
+}
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
   asm volatile(
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
@@ -645,8 +694,8 @@ __device__ __forceinline__ void tc_mma_pair_bf16(uint32_t d_tmem, uint64_t a_des
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -662,15 +711,16 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
   const uint32_t bars = stage0 + kPairStages * kPairStageBytes;
   uint8_t* bars_ptr = base_ptr + (bars - base);
   // barrier block (same offsets in both CTAs)
-  const uint32_t bar_full = bars;                          // [stages] weight halves landed (leader: both CTAs')
-  const uint32_t bar_empty = bars + 16 * kPairStages;      // [stages] slot consumed (multicast commit)
-  const uint32_t bar_acc = bars + 24 * kPairStages;        // layer accumulated (multicast commit)
-  const uint32_t bar_act = bar_acc + 8;                    // leader only: both epilogues done
-  const uint32_t bar_fc2 = bar_acc + 16;                   // peer's fc2 partial sums arrived
-  const uint32_t bar_in = bar_acc + 24;                    // peer's half of the next activations landed (bytes)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 24 * kPairStages + 40);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 24 * kPairStages + 44);
-  volatile int* epi_ok = reinterpret_cast<volatile int*>(bars_ptr + 24 * kPairStages + 48);
+  const uint32_t bar_full = bars;            // [stages <= 8] leader only: both CTAs' weight boxes landed
+  const uint32_t bar_empty = bars + 64;      // [stages <= 8] slot consumed (multicast commit)
+  const uint32_t bar_accj = bars + 128;      // [4] output block j accumulated (multicast commit)
+  const uint32_t bar_actq = bars + 160;      // [4] leader only: K quarter q of the activations ready in both CTAs
+  const uint32_t bar_inq = bars + 192;       // [4] peer's half of K quarter q landed here (bytes)
+  const uint32_t bar_tfree = bars + 224;     // [4] leader only: TMEM block j read out in both CTAs (8 warps)
+  const uint32_t bar_fc2 = bars + 256;       // peer's fc2 partial sums arrived
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 264);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 268);
+  volatile int* epi_ok = reinterpret_cast<volatile int*>(bars_ptr + 272);   // [2], one per epilogue group
   float* fc2_mine = reinterpret_cast<float*>(bars_ptr + 512);    // [64] own queries, own features
   float* fc2_peer = reinterpret_cast<float*>(bars_ptr + 768);    // [64] own queries, peer's features
 
@@ -682,13 +732,16 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
   if (threadIdx.x == 32) {
     for (int s = 0; s < kPairStages; ++s) {
       // leader: own arrive.expect_tx + the peer's forwarded arrive; peer: its own only
-      mbar_init(bar_full + 8 * s, rank == 0 ? 2 : 1);
+      mbar_init(bar_full + 8 * s, 1);   // used in the leader only: its producer's arrive.expect_tx
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_acc, 1);
-    mbar_init(bar_act, 2);
+    for (int q = 0; q < 4; ++q) {
+      mbar_init(bar_accj + 8 * q, 1);
+      mbar_init(bar_actq + 8 * q, 2);   // one arrive per CTA
+      mbar_init(bar_inq + 8 * q, 1);
+      mbar_init(bar_tfree + 8 * q, 8);  // one arrive per epilogue warp of the block, both CTAs
+    }
     mbar_init(bar_fc2, 1);
-    mbar_init(bar_in, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -728,29 +781,31 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
         size_t layer_base = 0;   // in tile images
         for (int L = 0; L < n_layers && ok; ++L) {
           const int nkb = L == 0 ? 1 : kNumKB;
-          // a ring slot takes two consecutive K blocks of one output block (fc1 has only one)
-          const int n_loads = (nkb + 1) / 2;
+          // A ring slot takes two consecutive K blocks of one output block (fc1 has only one);
+          // a hidden layer is streamed as 16 (block, K quarter) units of two slots each.
+          const int n_units = nkb == 1 ? kPairMT : 16;
+          const int n_loads = nkb == 1 ? 1 : 4 / kPairSlotKb;
           const uint32_t load_bytes = nkb == 1 ? kTileBytes : kPairStageBytes;
-          for (int j = 0; j < kPairMT && ok; ++j) {
-            const size_t blk = layer_base + static_cast<size_t>(2 * j + rank) * nkb;
-            for (int g = 0; g < n_loads; ++g, ++it) {
-              if (it % kPairStages != w) continue;
-              const uint32_t ph = (it / kPairStages) & 1u;
-              const long long q0 = ptimed ? clock64() : 0;
-              if (!mbar_wait(bar_empty + 8 * w, ph ^ 1u, abort_flag, p.status, 0x111)) { ok = false; break; }
-              const long long q1 = ptimed ? clock64() : 0;
-              mbar_expect_tx(bar_full + 8 * w, load_bytes);
-              bulk_g2s(stage0 + w * kPairStageBytes, p.wpack + (blk + 2 * g) * kTileBytes, load_bytes,
-                       bar_full + 8 * w);
-              issued = it + 1;
-              if (rank == 1) {
-                // the leader issues the MMAs: tell it when this CTA's half has landed
-                if (!mbar_wait(bar_full + 8 * w, ph, abort_flag, p.status, 0x112)) { ok = false; break; }
-                mbar_arrive_remote_plain(peer_full_leader);
-              }
-              if (ptimed) {
-                mbar_wait(bar_full + 8 * w, ph, abort_flag, p.status, 0x112);
-                pc_empty += q1 - q0; pc_copy += clock64() - q1; ++pc_n;
+          {
+            for (int u = 0; u < n_units && ok; ++u) {
+              const int j = nkb == 1 ? u : pair_unit_j(p.unit_order, u);
+              const int kq = nkb == 1 ? 0 : pair_unit_q(p.unit_order, u);
+              const size_t blk = layer_base + static_cast<size_t>(2 * j + rank) * nkb + kq * 4;
+              for (int g = 0; g < n_loads; ++g, ++it) {
+                if (it % kPairStages != w) continue;
+                const uint32_t ph = (it / kPairStages) & 1u;
+                const long long q0 = ptimed ? clock64() : 0;
+                if (!mbar_wait(bar_empty + 8 * w, ph ^ 1u, abort_flag, p.status, 0x111)) { ok = false; break; }
+                const long long q1 = ptimed ? clock64() : 0;
+                // both CTAs' boxes are counted on the leader's barrier
+                if (rank == 0) mbar_expect_tx(bar_full + 8 * w, 2 * load_bytes);
+                tma_rows_2sm(stage0 + w * kPairStageBytes, nkb == 1 ? &p.tmap_tile : &p.tmap_slot,
+                             static_cast<int32_t>((blk + kPairSlotKb * g) * (kTileBytes / 128)), peer_full_leader);
+                issued = it + 1;
+                if (ptimed) {
+                  mbar_wait(bar_full + 8 * w, ph, abort_flag, p.status, 0x112);
+                  pc_empty += q1 - q0; pc_copy += clock64() - q1; ++pc_n;
+                }
               }
             }
           }
@@ -760,8 +815,12 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
       if (ptimed) { p.phase_cycles[9] = pc_empty; p.phase_cycles[10] = pc_copy; p.phase_cycles[11] = pc_n; }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {
       // ------------------------------ MMA issuer (leader) -------------------
+      // The whole warp walks the loop and one elected lane issues: the operands of
+      // tcgen05.mma live in uniform registers, and a loop that only one lane of a
+      // diverged warp executes was measured at 645 cycles per eight MMAs against
+      // 512 (the tensor pipe's own rate) for the warp-uniform form.
       // D fp32, A/B bf16, A K-major, B MN-major (bit 16), N = 128, M = 256
       constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                  (static_cast<uint32_t>(kPairQ >> 3) << 17) |
@@ -770,58 +829,86 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
                                (static_cast<uint64_t>(2) << 61) | (static_cast<uint64_t>(1) << 16);
       const uint32_t a_lo0 = (stage0 & 0x3FFFF) >> 4;
       const uint32_t b_lo0 = (act & 0x3FFFF) >> 4;
-      uint32_t s = 0, ph = 0, lay = 0;
+      // par: bits 0-3 = parity of the next wait on bar_actq[q], bits 4-7 on bar_tfree[j]
+      uint32_t s = 0, ph = 0, par = 0;
       bool ok = true;
       const bool mtimed = p.phase_cycles != nullptr && blockIdx.x == 0;
-      long long mc_act = 0, mc_full = 0, mc_peer = 0, mc_issue = 0, mc_n = 0;
+      long long mc_act = 0, mc_full = 0, mc_tfree = 0, mc_issue = 0, mc_n = 0;
+      auto wait_flip = [&](uint32_t bar0, uint32_t idx, uint32_t bit, long long& acc, int code) -> bool {
+        const long long m0 = mtimed ? clock64() : 0;
+        const bool got = mbar_wait_cluster(bar0 + 8 * idx, (par >> bit) & 1u, abort_flag, p.status, code);
+        par ^= 1u << bit;
+        tc_fence_after();
+        if (mtimed) acc += clock64() - m0;
+        return got;
+      };
+      const long long k0 = clock64();
+      const unsigned long long g0 = global_timer_ns();
       for (int t = 0; t < my_tiles && ok; ++t) {
-        for (int L = 0; L < n_layers && ok; ++L, ++lay) {
-          const long long m0 = mtimed ? clock64() : 0;
-          if (!mbar_wait_cluster(bar_act, lay & 1u, abort_flag, p.status, 0x211)) { ok = false; break; }
-          tc_fence_after();
-          if (mtimed) mc_act += clock64() - m0;
+        for (int L = 0; L < n_layers && ok; ++L) {
           const int nkb = L == 0 ? 1 : kNumKB;
-          for (int j = 0; j < kPairMT && ok; ++j) {
+          const int n_units = nkb == 1 ? kPairMT : 16;
+          const int n_loads = nkb == 1 ? 1 : 4 / kPairSlotKb;
+          // fc1 reads K block 0, written after the previous tile's TMEM was read out
+          if (nkb == 1 && !wait_flip(bar_actq, 0, 0, mc_act, 0x211)) { ok = false; break; }
+          uint32_t seen = 0;   // bits 0-3: K quarters used, bits 4-7: blocks written, bits 8-15: units done per block
+          for (int u = 0; u < n_units && ok; ++u) {
+            const int j = nkb == 1 ? u : pair_unit_j(p.unit_order, u);
+            const int kq = nkb == 1 ? 0 : pair_unit_q(p.unit_order, u);
+            const bool first_of_block = ((seen >> (4 + j)) & 1u) == 0u;
+            if (nkb > 1) {
+              // first write into TMEM block j of this layer: the previous layer's values must be out
+              if (first_of_block && !wait_flip(bar_tfree, j, 4 + j, mc_tfree, 0x213)) { ok = false; break; }
+              // first use of K quarter kq
+              if (((seen >> kq) & 1u) == 0u && !wait_flip(bar_actq, kq, kq, mc_act, 0x211)) { ok = false; break; }
+            }
+            seen |= (1u << kq) | (16u << j);
+            // two-bit count of the block's earlier units; the fourth unit completes the block
+            const bool last_of_block = nkb == 1 || ((seen >> (8 + 2 * j)) & 3u) == 3u;
+            if (!last_of_block) seen += 1u << (8 + 2 * j);
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(j * kPairQ);
-            for (int g = 0; g < (nkb + 1) / 2; ++g) {
+            for (int g = 0; g < n_loads; ++g) {
               const long long m1 = mtimed ? clock64() : 0;
               if (!mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, 0x212)) { ok = false; break; }
               const long long m2 = mtimed ? clock64() : 0;
-              const long long m3 = m2;
-              tc_fence_after();
               const uint64_t a0 = desc_hi | (a_lo0 + s * (kPairStageBytes >> 4));
-              const uint64_t b0 = desc_hi | (b_lo0 + static_cast<uint32_t>(2 * g) * (kPairActKb >> 4));
-              // a K step of 16: 32 bytes along an A row, 16 K rows (2 KB) of B
-              tc_mma_pair_bf16(d_tmem, a0, b0, idesc, g != 0 ? 1u : 0u);
-              tc_mma_pair_bf16(d_tmem, a0 + 2, b0 + 128, idesc, 1u);
-              tc_mma_pair_bf16(d_tmem, a0 + 4, b0 + 256, idesc, 1u);
-              tc_mma_pair_bf16(d_tmem, a0 + 6, b0 + 384, idesc, 1u);
-              if (nkb > 1) {
-                // second K block of the slot: next weight tile (16 KB on), next 64 K rows (8 KB on)
-                const uint64_t a1 = a0 + (kTileBytes >> 4), b1 = b0 + (kPairActKb >> 4);
-                tc_mma_pair_bf16(d_tmem, a1, b1, idesc, 1u);
-                tc_mma_pair_bf16(d_tmem, a1 + 2, b1 + 128, idesc, 1u);
-                tc_mma_pair_bf16(d_tmem, a1 + 4, b1 + 256, idesc, 1u);
-                tc_mma_pair_bf16(d_tmem, a1 + 6, b1 + 384, idesc, 1u);
+              const uint64_t b0 = desc_hi | (b_lo0 + static_cast<uint32_t>(kq * 4 + kPairSlotKb * g) * (kPairActKb >> 4));
+              if (elect_one()) {
+                // a K step of 16: 32 bytes along an A row, 16 K rows (2 KB) of B
+                tc_mma_pair_bf16(d_tmem, a0, b0, idesc, (first_of_block && g == 0) ? 0u : 1u);
+                tc_mma_pair_bf16(d_tmem, a0 + 2, b0 + 128, idesc, 1u);
+                tc_mma_pair_bf16(d_tmem, a0 + 4, b0 + 256, idesc, 1u);
+                tc_mma_pair_bf16(d_tmem, a0 + 6, b0 + 384, idesc, 1u);
+                if (kPairSlotKb == 2 && nkb > 1) {
+                  // second K block of the slot: next weight tile (16 KB on), next 64 K rows (8 KB on)
+                  const uint64_t a1 = a0 + (kTileBytes >> 4), b1 = b0 + (kPairActKb >> 4);
+                  tc_mma_pair_bf16(d_tmem, a1, b1, idesc, 1u);
+                  tc_mma_pair_bf16(d_tmem, a1 + 2, b1 + 128, idesc, 1u);
+                  tc_mma_pair_bf16(d_tmem, a1 + 4, b1 + 256, idesc, 1u);
+                  tc_mma_pair_bf16(d_tmem, a1 + 6, b1 + 384, idesc, 1u);
+                }
+                tc_commit_pair(bar_empty + 8 * s);
+                if (last_of_block && g == n_loads - 1) tc_commit_pair(bar_accj + 8 * j);
               }
-              tc_commit_pair(bar_empty + 8 * s);
-              if (mtimed) { mc_full += m2 - m1; mc_peer += m3 - m2; mc_issue += clock64() - m3; ++mc_n; }
+              __syncwarp();
+              if (mtimed) { mc_full += m2 - m1; mc_issue += clock64() - m2; ++mc_n; }
               if (++s == kPairStages) { s = 0; ph ^= 1u; }
             }
           }
-          if (ok) tc_commit_pair(bar_acc);
         }
       }
-      if (mtimed) {
-        p.phase_cycles[4] = mc_act; p.phase_cycles[5] = mc_full; p.phase_cycles[6] = mc_peer;
+      if (mtimed && lane == 0) {
+        p.phase_cycles[4] = mc_act; p.phase_cycles[5] = mc_full; p.phase_cycles[6] = mc_tfree;
         p.phase_cycles[7] = mc_issue; p.phase_cycles[8] = mc_n;
+        p.phase_cycles[12] = clock64() - k0;
+        p.phase_cycles[13] = static_cast<long long>(global_timer_ns() - g0);
       }
     }
   } else if (warp >= 2) {
     // ------------------------------ epilogue ------------------------------
     // Two groups of four warps (warps 2-5 and 12-15); a warp may only read the
     // TMEM lane quadrant (warp id mod 4).  Group g drains the 256-feature blocks
-    // 2 g and 2 g + 1 of a layer, so both halves of TMEM are read at once.
+    // g and g + 2 of a hidden layer (2 g and 2 g + 1 under fc2).
     const int grp = warp >= 12 ? 1 : 0;
     const int e = (warp - (grp ? 12 : 2)) * 32 + lane;   // 0..127 inside the group
     const int T = grp * 128 + e;                         // 0..255 over both groups
@@ -830,13 +917,18 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const int C_in = p.n_op_feat + 4;
     const uint32_t act_peer = map_to_cta(act, peer);
-    const uint32_t bar_act_leader = map_to_cta(bar_act, 0);
-    const uint32_t bar_in_peer = map_to_cta(bar_in, peer);
-    uint32_t lay = 0, tile_no = 0, in_phase = 0;
+    uint32_t in_phase = 0, lay = 0, tile_no = 0;
     bool ok = true;
     float* red = reinterpret_cast<float*>(base_ptr);   // [256][33], aliases activations
     const bool timed = p.phase_cycles != nullptr && blockIdx.x == 0 && T == 0;
     long long c_wait = 0, c_epi = 0, c_fc2 = 0, c_layers = 0, c_ld = 0, c_bias = 0, c_sync = 0, c_loc = 0, c_rem = 0;
+    // named barrier of this group alone (ids 2 and 3; id 1 joins both groups)
+    auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory"); };
+    auto publish = [&](uint32_t q) {   // "this CTA's share of K quarter q is in place"
+      const uint32_t bar = bar_actq + 8 * q;
+      if (rank == 0) mbar_arrive(bar);
+      else mbar_arrive_remote(map_to_cta(bar, 0));
+    };
 
     for (int t = 0; t < my_tiles && ok; ++t, ++tile_no) {
       const int tile = pair_id + t * n_pairs;
@@ -869,39 +961,56 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
       }
       fence_proxy_async();
       pair_epi_bar_sync();
-      if (T == 0) {
-        if (rank == 0) mbar_arrive(bar_act);
-        else mbar_arrive_remote(bar_act_leader);
-      }
+      if (T == 0) publish(0);
 
       for (int L = 0; L < n_layers && ok; ++L, ++lay) {
-        const long long c0 = timed ? clock64() : 0;
-        if (T == 0) *epi_ok = mbar_wait(bar_acc, lay & 1u, abort_flag, p.status, 0x311) ? 1 : 0;
-        pair_epi_bar_sync();
-        if (*epi_ok == 0) { ok = false; break; }
-        tc_fence_after();
-        const long long c1 = timed ? clock64() : 0;
         const float* bias = p.bias + L * kWidth;
         const bool last = (L == n_layers - 1);
         if (!last) {
-          // the peer sends 512 K rows x 128 B of next-layer activations into this CTA
-          if (T == 0) mbar_expect_tx(bar_in, 512u * 128u);
+          // Group g drains output blocks g and g + 2.  Block j becomes K quarter j of the next
+          // layer and is written over the current activations in place: in the unit order of a
+          // hidden layer nothing reads quarter j once block j is complete.  Under fc1 the input
+          // sits in quarter 0 until the last block is done, so everything waits for that.
 #pragma unroll 1
           for (int jj = 0; jj < 2; ++jj) {
-            const int j = grp * 2 + jj;
+            const int j = grp + 2 * jj;
+            const int gate = L == 0 ? 3 : static_cast<int>((p.unit_gates >> (4 * j)) & 3u);
+            const long long c0 = timed ? clock64() : 0;
+            if (e == 0) {
+              epi_ok[grp] = mbar_wait(bar_accj + 8 * gate, lay & 1u, abort_flag, p.status, 0x311) ? 1 : 0;
+              // the peer sends 128 K rows x 128 B of this quarter into this CTA
+              mbar_expect_tx(bar_inq + 8 * j, 128u * 128u);
+            }
+            group_sync();
+            if (epi_ok[grp] == 0) { ok = false; break; }
+            tc_fence_after();
+            const long long c1 = timed ? clock64() : 0;
             const int f = j * 256 + static_cast<int>(rank) * 128 + r;   // feature = next layer's K index
             const long long d0 = timed ? clock64() : 0;
             const float b = __ldg(bias + f);
             if (timed) { c_bias += clock64() - d0 + static_cast<long long>(b == 12345.0f); }
             const uint32_t row_off = static_cast<uint32_t>(f) * 128u;   // K row f of the next layer's B operand
             const uint32_t sw = static_cast<uint32_t>(f) & 7u;
+            const uint32_t bar_in_peer = map_to_cta(bar_inq + 8 * j, peer);
+            const uint32_t bar_tfree_leader = map_to_cta(bar_tfree + 8 * j, 0);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {            // 64 queries = one CTA's share per load
+            for (int hh = 0; hh < 2; ++hh) {         // 64 queries = one CTA's share per load
+              // the peer's half first: it has the longer way to go
+              const bool mine = hh == 1;
+              const uint32_t h = mine ? rank : peer;
               float v[64];
               const long long d1 = timed ? clock64() : 0;
-              tc_ld64(t_lane + static_cast<uint32_t>(j * kPairQ + h * 64), v);
+              tc_ld64(t_lane + static_cast<uint32_t>(j * kPairQ) + h * 64u, v);
               if (timed) c_ld += clock64() - d1;
-              const bool mine = static_cast<uint32_t>(h) == rank;
+              if (mine) {
+                // this warp has read all of its lanes of block j: the next layer may overwrite them
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                  if (rank == 0) mbar_arrive(bar_tfree + 8 * j);
+                  else mbar_arrive_remote(bar_tfree_leader);
+                }
+              }
 #pragma unroll
               for (int g = 0; g < 8; ++g) {          // eight queries per 16-byte store
                 uint32_t w4[4];
@@ -917,21 +1026,26 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
               }
               if (timed) { if (mine) c_loc += clock64() - d1; else c_rem += clock64() - d1; }
             }
-          }
-          const long long d2 = timed ? clock64() : 0;
-          tc_fence_before();
-          asm volatile("fence.proxy.async;" ::: "memory");   // local and peer shared memory
-          pair_epi_bar_sync();
-          if (T == 0) {
-            // own stores are fenced above; the peer's arrive as counted bytes
-            if (mbar_wait_cluster(bar_in, in_phase, abort_flag, p.status, 0x313)) {
-              if (rank == 0) mbar_arrive(bar_act);
-              else mbar_arrive_remote(bar_act_leader);
+            const long long d2 = timed ? clock64() : 0;
+            tc_fence_before();
+            asm volatile("fence.proxy.async;" ::: "memory");   // local and peer shared memory
+            group_sync();
+            if (e == 0) {
+              // own stores are fenced above; the peer's arrive as counted bytes
+              if (mbar_wait_cluster(bar_inq + 8 * j, in_phase, abort_flag, p.status, 0x313))
+                publish(static_cast<uint32_t>(j));
             }
+            if (timed) { c_wait += c1 - c0; c_epi += clock64() - c1; c_sync += clock64() - d2; }
           }
           in_phase ^= 1u;
-          if (timed) { c_wait += c1 - c0; c_epi += clock64() - c1; ++c_layers; c_sync += clock64() - d2; }
+          if (timed) ++c_layers;
         } else {
+          const long long c0 = timed ? clock64() : 0;
+          if (T == 0) epi_ok[0] = mbar_wait(bar_accj + 8 * 3, lay & 1u, abort_flag, p.status, 0x311) ? 1 : 0;
+          pair_epi_bar_sync();
+          if (epi_ok[0] == 0) { ok = false; break; }
+          tc_fence_after();
+          const long long c1 = timed ? clock64() : 0;
           // fc2 over this CTA's 512 features, 32 queries at a time
 #pragma unroll 1
           for (int qd = 0; qd < 4; ++qd) {
@@ -973,10 +1087,10 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
           // hand-over of the partial sums, then the owner finishes its 64 queries
           if (T == 0) {
             mbar_arrive_remote(map_to_cta(bar_fc2, peer));
-            *epi_ok = mbar_wait_cluster(bar_fc2, tile_no & 1u, abort_flag, p.status, 0x312) ? 1 : 0;
+            epi_ok[0] = mbar_wait_cluster(bar_fc2, tile_no & 1u, abort_flag, p.status, 0x312) ? 1 : 0;
           }
           pair_epi_bar_sync();
-          if (*epi_ok == 0) { ok = false; break; }
+          if (epi_ok[0] == 0) { ok = false; break; }
           if (T < kPairHalfQ) {
             const int64_t q = q0 + T;
             if (q < p.Q) p.out[q] = fc2_mine[T] + fc2_peer[T] + p.fc2_b;
@@ -989,14 +1103,14 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
     if (timed) {
       p.phase_cycles[0] = c_wait; p.phase_cycles[1] = c_epi;
       p.phase_cycles[2] = c_fc2; p.phase_cycles[3] = c_layers;
-      p.phase_cycles[12] = c_ld; p.phase_cycles[13] = c_bias; p.phase_cycles[14] = c_sync; p.phase_cycles[15] = c_rem; p.phase_cycles[11] = c_loc;
+      p.phase_cycles[14] = c_sync; p.phase_cycles[15] = c_rem;
     }
   }
 
   // ------------------------------ teardown ------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp >= 6 && warp < 12 && lane == 0 && *abort_flag && warp - 6 < kPairStages && issued > 0) {
+  if (rank == 0 && warp >= 6 && warp < 12 && lane == 0 && *abort_flag && warp - 6 < kPairStages && issued > 0) {
     const uint32_t j = issued - 1;
     const uint32_t ph = (j / kPairStages) & 1u;
     const long long t0 = clock64();
@@ -1041,6 +1155,7 @@ struct hb_mlp {
   int32_t n_op_feat = 0, layers = 0, precision = 0, n_dev = 0, sm_count = 0, device = 0;
   float fc2_b = 0.f;
   uint8_t* wpack = nullptr;
+  CUtensorMap tmap_slot{}, tmap_tile{};
   float* bias = nullptr;
   float* fc2_w = nullptr;
   double* mu = nullptr;
@@ -1139,6 +1254,38 @@ extern "C" hb_status hb_mlp_create(hb_mlp** handle, int32_t n_op_features, int32
   HB_UP(sigma, sigma, sizeof(double) * C_in);
   HB_UP(dev_feat, device_features, sizeof(double) * 4 * n_device_rows);
 #undef HB_UP
+  {
+    // The pack as a 2-D tensor of 128-byte rows for the tiled TMA loads of the pair kernel.  The
+    // tile images are stored already swizzled, so the maps use no swizzle of their own.
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if ((e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres)) != cudaSuccess)
+      return fail(e, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+    if (fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+      hb::set_error("hb_mlp_create: the driver does not export cuTensorMapEncodeTiled");
+      hb_mlp_destroy(h);
+      return HB_ERR_CUDA;
+    }
+    const cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(pack.size() / 128)};
+    const cuuint64_t strides[1] = {128};
+    const cuuint32_t elem[2] = {1, 1};
+    for (int which = 0; which < 2; ++which) {
+      const cuuint32_t box[2] = {128, static_cast<cuuint32_t>((which == 0 ? kPairStageBytes : kTileBytes) / 128)};
+      const CUresult r = reinterpret_cast<EncodeFn>(fn)(
+          which == 0 ? &h->tmap_slot : &h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, h->wpack, dims, strides,
+          box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) {
+        hb::set_error("hb_mlp_create: cuTensorMapEncodeTiled failed (CUresult %d)", static_cast<int>(r));
+        hb_mlp_destroy(h);
+        return HB_ERR_CUDA;
+      }
+    }
+  }
   if ((e = cudaMalloc(reinterpret_cast<void**>(&h->status), sizeof(int32_t))) != cudaSuccess)
     return fail(e, "cudaMalloc status");
   if ((e = cudaMemset(h->status, 0, sizeof(int32_t))) != cudaSuccess) return fail(e, "cudaMemset");
@@ -1176,6 +1323,9 @@ extern "C" hb_status hb_mlp_predict(hb_mlp* h, const float* op_features, const u
   p.dev_row = device_row; p.Q = Q; p.out = out; p.num_tiles = static_cast<int32_t>(tiles);
   p.status = h->status;
   p.phase_cycles = h->phase_cycles;
+  p.tmap_slot = h->tmap_slot; p.tmap_tile = h->tmap_tile;
+  p.unit_order = kPairOrder;
+  p.unit_gates = kPairGates;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (split) {
     const int grid = static_cast<int>(tiles < h->sm_count ? tiles : h->sm_count);

@@ -198,11 +198,14 @@ hb_status hb_mlp_predict(hb_mlp* handle, const float* op_features, const uint8_t
 hb_status hb_mlp_status(hb_mlp* handle, int32_t* device_status);
 
 /* Profiling aid (bf16 kernel): SM cycle counters of the first cluster's leader CTA
- * for the most recent launch.  out[0..3] epilogue: waiting for a layer's MMAs,
- * draining hidden layers, fc2, layers counted.  out[4..8] MMA issuer: waiting for
- * activations, for its own weight copy, for the peer's, issuing, ring slots
- * counted.  out[9..11] first producer: waiting for a free slot, copy latency,
- * copies counted.  Synchronises.  No reference counterpart. */
+ * for the most recent launch.  out[0..3] first epilogue group: waiting for its
+ * output blocks, draining them, fc2, layers counted.  out[4..8] MMA issuer:
+ * waiting for activations, for weights, for TMEM blocks to be read out, issuing,
+ * ring slots counted.  out[9..11] first producer: waiting for a free slot, copy
+ * latency, copies counted.  out[12], out[13]: the MMA issuer's whole loop in SM
+ * cycles and in nanoseconds (their ratio is the SM clock under load).
+ * out[14], out[15] first epilogue group: hand-over of a drained block, stores
+ * into the peer CTA.  Synchronises.  No reference counterpart. */
 hb_status hb_mlp_phase_cycles(hb_mlp* handle, int64_t out[16]);
 
 /* Host-buffer form of hb_mlp_predict; also checks hb_mlp_status. */

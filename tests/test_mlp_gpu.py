@@ -108,3 +108,24 @@ def test_host_buffer_entry_point():
     ref = omlp.predict(w, feats, dev, DEVF, mu, sigma)
     assert _rel(got, ref).max() <= 2e-2
     h.close()
+
+
+@pytest.mark.parametrize("precision,Q", [("bf16", 74 * 128 * 3 + 77), ("bf16x3", 148 * 32 * 2 + 5)])
+def test_repeatable(precision, Q):
+    """The kernel's roles hand tiles, accumulators and activations to one another through
+    barriers; a missing hand-over shows as results that change from launch to launch long
+    before it breaks a tolerance.  Same inputs, several launches (each cluster walks more than
+    one tile): bit-identical outputs."""
+    w = workloads.init_mlp_weights("conv2d", seed=5, gain=np.sqrt(6.0))
+    feats, dev = workloads.make_queries("conv2d", Q, 31)
+    mu, sigma = workloads.batch_mu_sigma(feats, dev)
+    h = batched.MLPHandle(feats.shape[1], mu=mu, sigma=sigma, device_features=DEVF,
+                          precision=precision, **w)
+    f, r = torch.from_numpy(feats).cuda(), torch.from_numpy(dev).cuda()
+    first = h.predict(f, r).clone()
+    for _ in range(8):
+        again = h.predict(f, r)
+        assert torch.equal(first, again)
+    torch.cuda.synchronize()
+    h.check_status()
+    h.close()
