@@ -294,6 +294,7 @@ def main():
             ev[3].record(stream)
             torch.cuda.synchronize()
             kern_ms = ev[2].elapsed_time(ev[3]) / steps
+            wave_kernel = batched.wave_scale_path()     # which kernel the library chose for this launch
             pairs = WAVE_K * WAVE_D
             achieved = pairs * WAVE_BYTES_PER_PAIR / (kern_ms * 1e-3) / 1e9
 
@@ -328,7 +329,7 @@ def main():
                            "launch": "the timed steps are replayed from one CUDA graph; a step is the "
                                      "wave-scale kernel plus the per-destination totals",
                            "collective": "one all-reduce of the [steps x 6] totals" if world > 1 else "none"},
-                "roofline": {"bound": "hbm", "kernel": "wave_scale_class_kernel<2>",
+                "roofline": {"bound": "hbm", "kernel": wave_kernel,
                              "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                              "us_per_launch": kern_ms * 1e3,
@@ -384,6 +385,9 @@ def main():
             torch.cuda.synchronize()
             kern_ms = k0.elapsed_time(k1) / steps
             tflops = MLP_Q * MLP_FLOPS_PER_QUERY / (kern_ms * 1e-3) / 1e12
+            # SM clock inside the last launch: cycles and nanoseconds of the MMA issuer's loop
+            pc = handle.phase_cycles()
+            mlp_sm_mhz = 1e3 * pc["mma_total_cycles"] / pc["mma_total_ns"] if pc["mma_total_ns"] > 0 else None
 
             p_f, p_r = torch.from_numpy(feats).pin_memory(), torch.from_numpy(dev).pin_memory()
             mpipe = hostio.MLPPredictHost(handle, MLP_Q, depth=2)
@@ -410,6 +414,7 @@ def main():
                              "frac": tflops / peaks["bf16_tflops"],
                              "frac_of_sustained": tflops / peaks["bf16_tflops_sustained"],
                              "peak_source": peaks["source"], "ms_per_launch": kern_ms,
+                             "sm_mhz_in_kernel": mlp_sm_mhz,
                              "flops_per_query": MLP_FLOPS_PER_QUERY,
                              # dram__bytes_read + dram__bytes_write of one launch (ncu capture
                              # summarised in profiles/): weights once plus the queries

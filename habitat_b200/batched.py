@@ -147,6 +147,15 @@ def wave_scale(kernels: KernelBatch, origin, dests: Sequence, dest_regs=None, me
     return out
 
 
+WAVE_PATHS = {0: "none", 1: "wave_scale_kernel", 2: "wave_scale_fast_kernel", 3: "wave_scale_class_kernel",
+              4: "wave_scale_lut_kernel"}
+
+
+def wave_scale_path():
+    """Name of the kernel the calling thread's last wave_scale call launched."""
+    return WAVE_PATHS[int(_native.load().hb_wave_scale_path())]
+
+
 def wave_scale_host(arrays, origin, dests, want_status=False, want_limits=False):
     """Host-buffer path: numpy in, numpy out, transfers inside the native call."""
     lib = _native.load()

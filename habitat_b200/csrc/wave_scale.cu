@@ -23,6 +23,8 @@
 
 namespace {
 
+thread_local int32_t t_path = 0;   // kernel of the last launch, see hb_wave_scale_path
+
 __constant__ hb_dev_pre c_dev[HB_MAX_DEVICES];
 
 // Host mirror of the uploaded table (ratios are formed from the raw rows).
@@ -378,6 +380,13 @@ struct ClassParams {
 __device__ __forceinline__ int32_t pick_byte(uint32_t packed, uint32_t c) {
   return static_cast<int32_t>(__byte_perm(packed, 0u, 0x4440u | c));
 }
+// prmt.b32 in its default mode: selector nibble n picks byte (n & 7) of {b, a}; with bit 3 set
+// the byte's sign bit is replicated instead (0x00 for the values below 128 used here).
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -493,6 +502,176 @@ wave_scale_class_kernel(const Ptrs p, const __grid_constant__ ClassParams cp) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Table kernel.  The three class limits of a record are functions of small
+// integers: the register limit of (warps per block, 256-register units per
+// warp), the warp limit of the warps per block, the shared-memory limit of the
+// request in 128-byte steps.  hb_set_devices tabulates them per device row (one
+// byte each: anything above 127 cannot win against the blocks-per-SM limit) in
+// global memory; a launch reads the rows that represent its classes through
+// L1 (a few KB), so a record costs one byte load per class instead of the limit
+// arithmetic, and the kernel needs no shared memory and no block prologue.  The
+// reciprocals of the wave sizes (SMs x occupancy) and the log2 pairs of the
+// small-kernel branch are tabulated the same way.  A thread owns two consecutive
+// records and forms both occupancies of a destination with 16-bit-pair minimum
+// instructions; the destination loop is unrolled for up to eight destinations.
+// Conditions (checked on the host, else the class kernel runs): the class
+// kernel's own, plus K even, D K < 2^31, and per row 16 <= SMs, SMs x
+// blocks-per-SM limit inside the reciprocal table, thread limit per block a
+// multiple of 32 and <= 1024, shared-memory reserve a multiple of 128,
+// shared-memory cap below the table's last step, blocks-per-SM limit <= 127.
+// ---------------------------------------------------------------------------
+constexpr int kLutW = 34;      // warps per block 0..32, 33 = more
+constexpr int kLutU = 34;      // register units per warp 0..32, 33 = more than 256 registers
+constexpr int kLutS = 2048;    // shared memory in 128-byte steps, last entry = above every cap
+constexpr int kLutWPad = 36;
+
+__device__ uint8_t g_lut_r[HB_MAX_DEVICES][kLutW * kLutU];
+__device__ uint8_t g_lut_w[HB_MAX_DEVICES][kLutWPad];
+__device__ uint8_t g_lut_s[HB_MAX_DEVICES][kLutS];
+bool g_lut_ok[HB_MAX_DEVICES];   // host: row tabulated
+
+struct alignas(16) LutDev {       // three 16-byte groups, each fetched with one constant load
+  uint32_t sel_r, sel_w, sel_s;   // permute selectors: class byte of record 0 -> low half, record 1 -> high half
+  uint32_t bl2;                   // blocks-per-SM limit in both halves
+  float a_hi, a_lo, b_hi, b_lo;
+  int32_t num_sms;
+  uint32_t sms_magic;
+  float clk_hi, clk_lo;
+};
+struct LutDevRegs {               // LutDev as read by a thread
+  uint4 sel;                      // sel_r, sel_w, sel_s, bl2
+  float4 ab;                      // a_hi, a_lo, b_hi, b_lo
+  uint4 sm;                       // num_sms, sms_magic, clk_hi, clk_lo (bits)
+};
+__device__ __forceinline__ LutDevRegs load_lut_dev(const LutDev& d) {
+  LutDevRegs r;
+  r.sel = *reinterpret_cast<const uint4*>(&d.sel_r);
+  r.ab = *reinterpret_cast<const float4*>(&d.a_hi);
+  r.sm = *reinterpret_cast<const uint4*>(&d.num_sms);
+  return r;
+}
+
+struct LutParams {
+  int32_t D, n_rc, n_wc, n_sc;
+  int64_t K;
+  int32_t row_r[kMaxClasses], row_w[kMaxClasses], row_s[kMaxClasses];   // table rows of the classes
+  LutDev origin;
+  LutDev dest[HB_MAX_DEVICES / 2];
+};
+
+constexpr int kLutThreads = 128;
+
+__device__ float2 g_log2_pair[33];     // log2(i) as float hi + lo; filled by hb_set_devices
+constexpr int kWaveMagicN = 8192;      // wave sizes (SMs x occupancy) below this have a tabulated reciprocal
+__device__ uint32_t g_wave_magic[kWaveMagicN];
+
+// floor(n / d) for d >= 2 with M = floor(2^32 / d) + 1 and any n < 2^32.
+__device__ __forceinline__ uint32_t udiv_fix_ge2(uint32_t n, uint32_t d, uint32_t M) {
+  uint32_t q = __umulhi(n, M);
+  if (q * d > n) --q;
+  return q;
+}
+
+template <int DS, int MINB>   // DS > 0: destination count known at compile time, 0: run time
+__global__ void __launch_bounds__(kLutThreads, MINB)
+wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
+  const int D = DS > 0 ? DS : lp.D;
+  const int64_t K = lp.K;
+  const int64_t k0 = (static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x) * 2;
+  if (k0 >= K) return;
+
+  const Vec<int32_t, 2> nbv = load_vec<int32_t, 2>(p.num_blocks + k0);
+  const Vec<uint16_t, 2> bsv = load_vec<uint16_t, 2>(p.block_size + k0);
+  const Vec<uint16_t, 2> rgv = load_vec<uint16_t, 2>(p.regs + k0);
+  const Vec<uint32_t, 2> smv = load_vec<uint32_t, 2>(p.smem + k0);
+  const Vec<float, 2> tv = load_vec<float, 2>(p.time_ns + k0);
+  const Vec<float, 2> gv = load_vec<float, 2>(p.gamma + k0);
+
+  uint32_t lr[2], lw[2], ls[2];
+  int32_t wave_o[2];
+  float2 lg_o[2];
+  float omg[2];
+  bool live[2], lt_o[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const uint32_t wpb = min((static_cast<uint32_t>(bsv.v[i]) + 31u) >> 5, static_cast<uint32_t>(kLutW - 1));
+    const uint32_t units = min((static_cast<uint32_t>(rgv.v[i]) + 7u) >> 3, static_cast<uint32_t>(kLutU - 1));
+    const uint32_t steps = min((min(smv.v[i], static_cast<uint32_t>(kLutS) << 7) + 127u) >> 7,
+                               static_cast<uint32_t>(kLutS - 1));
+    uint32_t r = 0, w = 0, sm = 0;
+#pragma unroll
+    for (int c = 0; c < kMaxClasses; ++c) {
+      if (c < lp.n_rc) r |= static_cast<uint32_t>(__ldg(&g_lut_r[lp.row_r[c]][wpb * kLutU + units])) << (8 * c);
+      if (c < lp.n_wc) w |= static_cast<uint32_t>(__ldg(&g_lut_w[lp.row_w[c]][wpb])) << (8 * c);
+      if (c < lp.n_sc) sm |= static_cast<uint32_t>(__ldg(&g_lut_s[lp.row_s[c]][steps])) << (8 * c);
+    }
+    lr[i] = r; lw[i] = w; ls[i] = sm;
+    omg[i] = 1.0f - gv.v[i];
+  }
+  // origin: both records at once
+  const LutDevRegs og = load_lut_dev(lp.origin);
+  const int32_t o_sms = static_cast<int32_t>(og.sm.x);
+  const uint32_t o2 = __vimin3_s16x2(
+      __vimin3_s16x2(prmt(lr[0], lr[1], og.sel.x), prmt(ls[0], ls[1], og.sel.z), prmt(lw[0], lw[1], og.sel.y)),
+      og.sel.w, og.sel.w);
+  Vec<uint32_t, 2> owav;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const uint32_t occ = i == 0 ? (o2 & 0xFFFFu) : (o2 >> 16);
+    const int32_t nb = nbv.v[i];
+    wave_o[i] = o_sms * static_cast<int32_t>(occ);
+    owav.v[i] = (occ > 0 && nb >= 1)
+                    ? udiv_fix_ge2(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_o[i]),
+                                   __ldg(&g_wave_magic[wave_o[i]]))
+                    : 0xFFFFFFFFu;
+    live[i] = nb >= 1 && occ != 0;
+    lt_o[i] = nb < wave_o[i];
+    // ceil(nb / num_sms) <= occupancy <= 32 whenever the small-kernel branch is taken
+    const uint32_t om = (nb >= 1 && lt_o[i]) ? __umulhi(nb + o_sms - 1, og.sm.y) : 1u;
+    lg_o[i] = __ldg(&g_log2_pair[om]);
+  }
+  *reinterpret_cast<uint16_t*>(p.origin_occ + k0) = static_cast<uint16_t>(__byte_perm(o2, 0u, 0x4420u));
+  store_vec<uint32_t, 2>(p.origin_waves + k0, owav);
+
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    const LutDevRegs dd = load_lut_dev(lp.dest[d]);
+    const int32_t d_sms = static_cast<int32_t>(dd.sm.x);
+    const float clk_hi = __uint_as_float(dd.sm.z), clk_lo = __uint_as_float(dd.sm.w);
+    const uint32_t base = static_cast<uint32_t>(d) * static_cast<uint32_t>(K) + static_cast<uint32_t>(k0);   // D K < 2^31
+    const uint32_t occ2 = __vimin3_s16x2(
+        __vimin3_s16x2(prmt(lr[0], lr[1], dd.sel.x), prmt(ls[0], ls[1], dd.sel.z), prmt(lw[0], lw[1], dd.sel.y)),
+        dd.sel.w, dd.sel.w);
+    Vec<float, 2> outv;
+    Vec<uint32_t, 2> wavv;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint32_t occ = i == 0 ? (occ2 & 0xFFFFu) : (occ2 >> 16);
+      const int32_t nb = nbv.v[i];
+      const int32_t wave_d = d_sms * static_cast<int32_t>(occ);
+      wavv.v[i] = (occ > 0 && nb >= 1)
+                      ? udiv_fix_ge2(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_d),
+                                     __ldg(&g_wave_magic[wave_d]))
+                      : 0xFFFFFFFFu;
+      const float gamma = gv.v[i];
+      const bool small = live[i] && lt_o[i] && nb < wave_d;
+      const bool ok = live[i] && !(lt_o[i] && occ == 0);
+      // small kernel (roofline.py:32-45): exponent (1 - gamma) (log2 clk + log2 dmax - log2 omax),
+      // both per-SM block counts <= 32; log2 values carried as float hi + lo
+      const uint32_t dm = small ? __umulhi(nb + d_sms - 1, dd.sm.y) : 1u;
+      const float2 lg_d = __ldg(&g_log2_pair[dm]);
+      const float e_small = omg[i] * ((lg_d.x - lg_o[i].x) + ((lg_d.y - lg_o[i].y) + clk_lo) + clk_hi);
+      const float e_large = fmaf(gamma, dd.ab.x, dd.ab.z) + fmaf(gamma, dd.ab.y, dd.ab.w);
+      const float e = small ? e_small : e_large;
+      outv.v[i] = ok ? tv.v[i] * ex2_approx(e) : __int_as_float(0x7FC00000);
+    }
+    store_vec<float, 2>(p.scaled_ns + base, outv);
+    *reinterpret_cast<uint16_t*>(p.dest_occ + base) = static_cast<uint16_t>(__byte_perm(occ2, 0u, 0x4420u));
+    store_vec<uint32_t, 2>(p.dest_waves + base, wavv);
+  }
+}
+
 // Finds (or appends) the class of `f` under `same`; returns -1 when full.
 template <typename Same>
 int class_of(FastDev* classes, int32_t* n, const FastDev& f, Same same) {
@@ -527,6 +706,96 @@ bool build_class_params(const FastParams& fp, ClassParams* cp) {
   return true;
 }
 
+// Whether a row can be tabulated for wave_scale_lut_kernel.
+bool lut_row_ok(const hb_device_spec& s, const hb_dev_pre& pre) {
+  return fast_row_ok(s, pre) && s.num_sms >= 16 && s.num_sms * pre.blocks_limit < kWaveMagicN && pre.max_threads_per_block % 32 == 0 &&
+         pre.max_threads_per_block <= 1024 && pre.smem_reserved % 128 == 0 &&
+         pre.smem_cap <= (kLutS - 2) * 128 && pre.blocks_limit <= 127;
+}
+
+// Tabulates the three limits of one device row (host side of hb_set_devices).
+void build_row_lut(const FastDev& f, uint8_t* r, uint8_t* w, uint8_t* sm, const uint32_t* magic) {
+  auto clamp = [](int32_t v) { return static_cast<uint8_t>(v < 0 ? 0 : (v > 127 ? 127 : v)); };
+  for (int wpb = 0; wpb < kLutW; ++wpb) {
+    FastKernel k{};
+    k.block_size = wpb * 32;
+    k.wpb = wpb;
+    k.m_wpb = magic_of(static_cast<uint32_t>(wpb));
+    w[wpb] = clamp(fast_warps_limit(f, k));
+    for (int u = 0; u < kLutU; ++u) {
+      k.regs = u * 8;          // any count with this many 256-register units per warp
+      k.rpw_units = u;
+      r[wpb * kLutU + u] = wpb == 0 ? 0 : clamp(fast_regs_limit(f, k, k.regs, u, magic_of(static_cast<uint32_t>(u))));
+    }
+  }
+  for (int i = kLutW; i < kLutWPad; ++i) w[i] = 0;
+  for (int st = 0; st < kLutS; ++st) {
+    FastKernel k{};
+    k.smem = st * 128;         // the largest request of this 128-byte step
+    sm[st] = st == kLutS - 1 ? 0 : clamp(fast_smem_limit(f, k, magic));
+  }
+}
+
+uint32_t pair_selector(int c) {
+  const uint32_t lo = static_cast<uint32_t>(c), hi = static_cast<uint32_t>(4 + c);
+  return lo | ((8u | lo) << 4) | (hi << 8) | ((8u | hi) << 12);
+}
+
+// Launches wave_scale_lut_kernel when the launch qualifies; false = nothing launched.
+bool try_launch_lut(const Ptrs& p, const FastParams& fp, const ClassParams& cp, const LaunchParams& lp,
+                    cudaStream_t stream, hb_status* st) {
+  const int64_t K = fp.K;
+  auto al = [](const void* q, uintptr_t a) { return (reinterpret_cast<uintptr_t>(q) & (a - 1)) == 0; };
+  if (K % 2 != 0 || !al(p.num_blocks, 8) || !al(p.smem, 8) || !al(p.time_ns, 8) || !al(p.gamma, 8) ||
+      !al(p.block_size, 4) || !al(p.regs, 4) || !al(p.scaled_ns, 8) || !al(p.dest_waves, 8) ||
+      !al(p.origin_waves, 8) || !al(p.dest_occ, 2) || !al(p.origin_occ, 2))
+    return false;
+  if (static_cast<int64_t>(lp.D) * K >= (int64_t{1} << 31)) return false;   // 32-bit element indices
+  if (!g_lut_ok[lp.origin_row]) return false;
+  for (int d = 0; d < lp.D; ++d)
+    if (!g_lut_ok[lp.dest_row[d]]) return false;
+
+  LutParams q{};
+  q.D = cp.D; q.K = K; q.n_rc = cp.n_rc; q.n_wc = cp.n_wc; q.n_sc = cp.n_sc;
+  // a class is represented by the first row of the launch that belongs to it
+  bool have_r[kMaxClasses] = {}, have_w[kMaxClasses] = {}, have_s[kMaxClasses] = {};
+  for (int d = -1; d < lp.D; ++d) {
+    const ClassDev& c = d < 0 ? cp.origin : cp.dest[d];
+    const int row = d < 0 ? lp.origin_row : lp.dest_row[d];
+    if (!have_r[c.rc]) { have_r[c.rc] = true; q.row_r[c.rc] = row; }
+    if (!have_w[c.wc]) { have_w[c.wc] = true; q.row_w[c.wc] = row; }
+    if (!have_s[c.sc]) { have_s[c.sc] = true; q.row_s[c.sc] = row; }
+    LutDev& o = d < 0 ? q.origin : q.dest[d];
+    o.num_sms = c.num_sms; o.sms_magic = c.sms_magic;
+    o.a_hi = c.a_hi; o.a_lo = c.a_lo; o.b_hi = c.b_hi; o.b_lo = c.b_lo;
+    o.clk_hi = c.clk_hi; o.clk_lo = c.clk_lo;
+    o.sel_r = pair_selector(c.rc); o.sel_w = pair_selector(c.wc); o.sel_s = pair_selector(c.sc);
+    o.bl2 = static_cast<uint32_t>(c.blocks_limit) * 0x00010001u;
+  }
+
+  const int64_t blocks = (K / 2 + kLutThreads - 1) / kLutThreads;
+  if (blocks > 0x7FFFFFFF || blocks < 1) return false;
+  const unsigned grid = static_cast<unsigned>(blocks);
+  // 12 blocks of 128 threads per SM (40 registers) measured fastest; 8, 10 and 16 were slower
+#define HB_LUT_LAUNCH(DS) wave_scale_lut_kernel<DS, 12><<<grid, kLutThreads, 0, stream>>>(p, q);
+  switch (q.D) {
+    case 1: HB_LUT_LAUNCH(1) break;
+    case 2: HB_LUT_LAUNCH(2) break;
+    case 3: HB_LUT_LAUNCH(3) break;
+    case 4: HB_LUT_LAUNCH(4) break;
+    case 5: HB_LUT_LAUNCH(5) break;
+    case 6: HB_LUT_LAUNCH(6) break;
+    case 7: HB_LUT_LAUNCH(7) break;
+    case 8: HB_LUT_LAUNCH(8) break;
+    default: HB_LUT_LAUNCH(0) break;
+  }
+#undef HB_LUT_LAUNCH
+  t_path = 4;
+  const cudaError_t ce = cudaGetLastError();
+  *st = ce == cudaSuccess ? HB_OK : hb::cuda_fail(ce, "wave_scale_lut_kernel launch");
+  return true;
+}
+
 // Fast path when every row of the launch qualifies and only the five standard
 // outputs are wanted; returns false (nothing launched) otherwise.
 bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream, hb_status* st) {
@@ -558,6 +827,8 @@ bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream,
   }
   ClassParams cp;
   if (!p.dest_regs && build_class_params(fp, &cp)) {
+    static const bool use_lut = [] { const char* e = std::getenv("HB_WAVE_LUT"); return !e || std::atoi(e) != 0; }();
+    if (use_lut && try_launch_lut(p, fp, cp, lp, stream, st)) return true;
     const int cthreads = 128;
     static const int vec_pref = [] { const char* e = std::getenv("HB_WAVE_VEC"); return e ? std::atoi(e) : 2; }();
     // two records per thread measured fastest (more resident warps than four per thread)
@@ -567,6 +838,7 @@ bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream,
       if (cvec == 4) wave_scale_class_kernel<4><<<static_cast<unsigned>(cblocks), cthreads, 0, stream>>>(p, cp);
       else if (cvec == 2) wave_scale_class_kernel<2><<<static_cast<unsigned>(cblocks), cthreads, 0, stream>>>(p, cp);
       else wave_scale_class_kernel<1><<<static_cast<unsigned>(cblocks), cthreads, 0, stream>>>(p, cp);
+      t_path = 3;
       const cudaError_t ce = cudaGetLastError();
       *st = ce == cudaSuccess ? HB_OK : hb::cuda_fail(ce, "wave_scale_class_kernel launch");
       return true;
@@ -580,6 +852,7 @@ bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream,
     if (p.dest_regs) wave_scale_fast_kernel<1, true><<<grid, threads, 0, stream>>>(p, fp);
     else wave_scale_fast_kernel<1, false><<<grid, threads, 0, stream>>>(p, fp);
   }
+  t_path = 2;
   const cudaError_t e = cudaGetLastError();
   *st = e == cudaSuccess ? HB_OK : hb::cuda_fail(e, "wave_scale_fast_kernel launch");
   return true;
@@ -610,6 +883,7 @@ hb_status launch(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream) {
     if (extra) wave_scale_kernel<1, METRICS, true><<<grid, threads, 0, stream>>>(p, lp);
     else wave_scale_kernel<1, METRICS, false><<<grid, threads, 0, stream>>>(p, lp);
   }
+  t_path = 1;
   HB_CUDA_TRY(cudaGetLastError());
   return HB_OK;
 }
@@ -690,6 +964,8 @@ Ptrs make_ptrs(const hb_kernel_soa* k, const hb_kernel_metrics* m, const int16_t
 
 }  // namespace
 
+extern "C" int32_t hb_wave_scale_path(void) { return t_path; }
+
 extern "C" hb_status hb_set_devices(const hb_device_spec* rows, int32_t n) {
   if (!rows || n < 1 || n > HB_MAX_DEVICES) {
     hb::set_error("hb_set_devices: need 1..%d rows", HB_MAX_DEVICES);
@@ -713,6 +989,28 @@ extern "C" hb_status hb_set_devices(const hb_device_spec* rows, int32_t n) {
   uint32_t magic[kMagicN];
   for (int i = 0; i < kMagicN; ++i) magic[i] = magic_of(static_cast<uint32_t>(i));
   HB_CUDA_TRY(cudaMemcpyToSymbol(g_magic, magic, sizeof(magic)));
+  {
+    std::vector<uint8_t> r(static_cast<size_t>(n) * kLutW * kLutU), w(static_cast<size_t>(n) * kLutWPad),
+        sm(static_cast<size_t>(n) * kLutS);
+    for (int i = 0; i < n; ++i) {
+      g_lut_ok[i] = lut_row_ok(g_rows[i], g_pre[i]);
+      if (g_lut_ok[i])
+        build_row_lut(fold_fast(g_rows[i], g_pre[i]), &r[static_cast<size_t>(i) * kLutW * kLutU],
+                      &w[static_cast<size_t>(i) * kLutWPad], &sm[static_cast<size_t>(i) * kLutS], magic);
+    }
+    float2 lp2[33];
+    for (int i = 0; i < 33; ++i) {
+      const float hi = static_cast<float>(lg[i]);
+      lp2[i] = make_float2(hi, static_cast<float>(lg[i] - static_cast<double>(hi)));
+    }
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_log2_pair, lp2, sizeof(lp2)));
+    std::vector<uint32_t> wm(kWaveMagicN);
+    for (int i = 0; i < kWaveMagicN; ++i) wm[i] = magic_of(static_cast<uint32_t>(i));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_wave_magic, wm.data(), wm.size() * sizeof(uint32_t)));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_r, r.data(), r.size()));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_w, w.data(), w.size()));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_s, sm.data(), sm.size()));
+  }
   return HB_OK;
 }
 

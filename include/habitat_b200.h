@@ -144,6 +144,12 @@ hb_status hb_wave_scale_metrics(const hb_kernel_soa* kernels, const hb_kernel_me
                                 int32_t D, const int16_t* dest_regs, const hb_wave_out* out,
                                 void* stream);
 
+/* Which kernel the calling thread's most recent hb_wave_scale / hb_wave_scale_metrics call
+ * launched: 0 none yet, 1 generic (any device row, status / limits / metrics outputs),
+ * 2 division-free, 3 per-limit device classes, 4 tabulated limits.  For tests and for
+ * naming the measured kernel; no reference counterpart. */
+int32_t hb_wave_scale_path(void);
+
 /* Host-buffer form of hb_wave_scale: all pointers in `kernels`, `dest_regs`
  * and `out` are HOST pointers; transfers happen inside the call. */
 hb_status hb_wave_scale_host(const hb_kernel_soa* kernels, int64_t K, int32_t origin_row,

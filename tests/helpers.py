@@ -36,6 +36,7 @@ def run_wave_gpu(kernels, origin, dests, dest_regs=None, metrics=None):
         # the same call without the verification outputs takes the division-free kernel
         fast = batched.wave_scale(kb, origin, dests, dest_regs=dr)
         torch.cuda.synchronize()
+        out["fast_path"] = batched.wave_scale_path()
         out["fast"] = {k: to_numpy(getattr(fast, k)) for k in
                        ("scaled_ns", "dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves")}
     return out

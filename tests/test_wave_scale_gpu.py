@@ -141,3 +141,62 @@ def test_reductions():
     ref = np.maximum(rt.astype(np.float64) * pd / po, 0).astype(np.float32)
     assert np.array_equal(got, ref)
     assert int(cnt.view(torch.int32).cpu()[0]) == int((rt.astype(np.float64) * pd / po < 0).sum())
+
+
+def _edge_records(devices):
+    """Records on and around every boundary the tabulated limits are indexed by."""
+    g = np.random.default_rng(77)
+    blocks, block_size, regs, smem = [], [], [], []
+
+    def add(nb, bs, rg, sm):
+        blocks.append(nb); block_size.append(bs); regs.append(rg); smem.append(sm)
+
+    for bs in list(range(0, 1100)) + [2048, 4096, 65535]:             # every warps-per-block step and beyond
+        add(int(g.integers(1, 5000)), bs, int(g.integers(0, 300)), int(g.integers(0, 100_000)))
+    for rg in list(range(0, 330)) + [512, 1000, 65535]:                # every register step, above 256 too
+        add(int(g.integers(1, 5000)), int(g.choice([32, 96, 128, 256, 1000, 1024])), rg, int(g.integers(0, 60_000)))
+    for sm in range(0, 262_400, 61):                                   # odd offsets across every 128-byte step
+        add(int(g.integers(1, 5000)), int(g.choice([64, 256, 1024])), int(g.integers(0, 128)), sm)
+    for step in range(0, 2060, 7):                                     # exactly on, below and above step edges
+        for delta in (-1, 0, 1):
+            add(77, 128, 32, max(0, step * 128 + delta))
+    for sm in (0xFFFFFFFF, 0x80000000, 0x7FFF0001, 0x7FFF0000, 262_143, 262_144, 262_145):
+        add(5, 128, 32, sm)
+    # grid sizes around the wave sizes (SMs x occupancy) of every row, and the extremes
+    for dev in devices:
+        for occ in (1, 2, 3, 8, 16, 32):
+            wave = dev.num_sms * occ
+            for nb in (wave - 1, wave, wave + 1, 2 * wave - 1, 2 * wave, dev.num_sms - 1, dev.num_sms, dev.num_sms + 1):
+                add(nb, int(g.choice([32, 64, 128, 256, 512, 1024])), int(g.integers(16, 128)),
+                    int(g.integers(0, 48 * 1024)))
+    for nb in (0, -1, -5, 1, 2, 2**31 - 1, 2**31 - 2, 2**30, 2**30 + 12345, 29_000_000, 29_100_000, 123_456_789):
+        for bs in (32, 256, 1024):
+            add(nb, bs, 32, 1024)
+    n = len(blocks) + (len(blocks) & 1)                                # the tabulated kernel takes even K
+    while len(blocks) < n:
+        add(1, 32, 16, 0)
+    return dict(
+        num_blocks=np.array(blocks, np.int64).astype(np.int32),
+        block_size=np.array(block_size, np.uint16), regs_per_thread=np.array(regs, np.uint16),
+        smem_bytes=np.array(smem, np.uint64).astype(np.uint32),
+        run_time_ns=np.exp(g.uniform(np.log(2e3), np.log(5e7), size=n)).astype(np.float64),
+        gamma=g.uniform(0.0, 1.0, size=n).astype(np.float32))
+
+
+def test_tabulated_kernel_on_edges(bench_devices, device_file):
+    """The table kernel (taken for even K when every row qualifies) against the oracle on records
+    that sit on, just below and just above every index boundary of its tables."""
+    kernels = _edge_records(bench_devices)
+    for origin in bench_devices:
+        got = run_wave_gpu(kernels, origin, bench_devices)
+        assert got["fast_path"] == "wave_scale_lut_kernel"
+        assert_wave_equal(got, run_wave_oracle(kernels, origin, bench_devices))
+    # other rows of the device file, in groups small enough to stay within four classes per limit
+    names = sorted(device_file)
+    taken = 0
+    for i in range(0, len(names) - 2, 3):
+        devs = [device_file[n] for n in names[i:i + 3]]
+        got = run_wave_gpu(kernels, devs[0], devs)
+        taken += got["fast_path"] == "wave_scale_lut_kernel"
+        assert_wave_equal(got, run_wave_oracle(kernels, devs[0], devs))
+    assert taken >= 2
