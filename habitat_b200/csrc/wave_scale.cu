@@ -514,7 +514,7 @@ wave_scale_class_kernel(const Ptrs p, const __grid_constant__ ClassParams cp) {
 // reciprocals of the wave sizes (SMs x occupancy) and the log2 pairs of the
 // small-kernel branch are tabulated the same way.  A thread owns two consecutive
 // records and forms both occupancies of a destination with 16-bit-pair minimum
-// instructions; the destination loop is unrolled for up to eight destinations.
+// instructions.
 // Conditions (checked on the host, else the class kernel runs): the class
 // kernel's own, plus K even, D K < 2^31, and per row 16 <= SMs, SMs x
 // blocks-per-SM limit inside the reciprocal table, thread limit per block a
@@ -573,10 +573,11 @@ __device__ __forceinline__ uint32_t udiv_fix_ge2(uint32_t n, uint32_t d, uint32_
   return q;
 }
 
-template <int DS, int MINB>   // DS > 0: destination count known at compile time, 0: run time
-__global__ void __launch_bounds__(kLutThreads, MINB)
+// 12 blocks of 128 threads per SM (40 registers) measured fastest (8, 10 and 16 were slower), and
+// so did the run-time destination loop against instances unrolled for a known destination count.
+__global__ void __launch_bounds__(kLutThreads, 12)
 wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
-  const int D = DS > 0 ? DS : lp.D;
+  const int D = lp.D;
   const int64_t K = lp.K;
   const int64_t k0 = (static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x) * 2;
   if (k0 >= K) return;
@@ -634,7 +635,7 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
   *reinterpret_cast<uint16_t*>(p.origin_occ + k0) = static_cast<uint16_t>(__byte_perm(o2, 0u, 0x4420u));
   store_vec<uint32_t, 2>(p.origin_waves + k0, owav);
 
-#pragma unroll
+#pragma unroll 1
   for (int d = 0; d < D; ++d) {
     const LutDevRegs dd = load_lut_dev(lp.dest[d]);
     const int32_t d_sms = static_cast<int32_t>(dd.sm.x);
@@ -777,19 +778,7 @@ bool try_launch_lut(const Ptrs& p, const FastParams& fp, const ClassParams& cp, 
   if (blocks > 0x7FFFFFFF || blocks < 1) return false;
   const unsigned grid = static_cast<unsigned>(blocks);
   // 12 blocks of 128 threads per SM (40 registers) measured fastest; 8, 10 and 16 were slower
-#define HB_LUT_LAUNCH(DS) wave_scale_lut_kernel<DS, 12><<<grid, kLutThreads, 0, stream>>>(p, q);
-  switch (q.D) {
-    case 1: HB_LUT_LAUNCH(1) break;
-    case 2: HB_LUT_LAUNCH(2) break;
-    case 3: HB_LUT_LAUNCH(3) break;
-    case 4: HB_LUT_LAUNCH(4) break;
-    case 5: HB_LUT_LAUNCH(5) break;
-    case 6: HB_LUT_LAUNCH(6) break;
-    case 7: HB_LUT_LAUNCH(7) break;
-    case 8: HB_LUT_LAUNCH(8) break;
-    default: HB_LUT_LAUNCH(0) break;
-  }
-#undef HB_LUT_LAUNCH
+  wave_scale_lut_kernel<<<grid, kLutThreads, 0, stream>>>(p, q);
   t_path = 4;
   const cudaError_t ce = cudaGetLastError();
   *st = ce == cudaSuccess ? HB_OK : hb::cuda_fail(ce, "wave_scale_lut_kernel launch");
