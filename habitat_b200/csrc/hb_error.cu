@@ -1,4 +1,6 @@
 // Error text and version of the library.
+#include <cstdlib>
+
 #include "hb_common.h"
 
 namespace {
@@ -11,6 +13,13 @@ void set_error(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(t_error, sizeof(t_error), fmt, ap);
   va_end(ap);
+}
+bool overlapped_launch_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("HB_NO_OVERLAPPED_LAUNCH");
+    return !(e && e[0] && e[0] != '0');
+  }();
+  return on;
 }
 }  // namespace hb
 

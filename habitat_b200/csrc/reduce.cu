@@ -57,6 +57,7 @@ constexpr int kPlaneBlocks = 256;
 __global__ void __launch_bounds__(kSumThreads)
 plane_partial_kernel(const float* __restrict__ values, int64_t plane_len,
                      double* __restrict__ partial) {
+  hb_grid_dependency_wait();
   const int plane = blockIdx.y;
   const float* v = values + static_cast<int64_t>(plane) * plane_len;
   const int64_t chunk = (plane_len + kPlaneBlocks - 1) / kPlaneBlocks;
@@ -73,6 +74,7 @@ plane_partial_kernel(const float* __restrict__ values, int64_t plane_len,
 
 __global__ void __launch_bounds__(kSumThreads)
 plane_final_kernel(const double* __restrict__ partial, double* __restrict__ out) {
+  hb_grid_dependency_wait();
   const int plane = blockIdx.x;
   const double v = threadIdx.x < kPlaneBlocks ? partial[plane * kPlaneBlocks + threadIdx.x] : 0.0;
   const double t = block_sum(v);
@@ -135,11 +137,10 @@ extern "C" hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_
     g_partial_planes = n_planes;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  plane_partial_kernel<<<dim3(kPlaneBlocks, n_planes), kSumThreads, 0, s>>>(values, plane_len,
-                                                                            g_partial);
-  HB_CUDA_TRY(cudaGetLastError());
-  plane_final_kernel<<<n_planes, kSumThreads, 0, s>>>(g_partial, out);
-  HB_CUDA_TRY(cudaGetLastError());
+  HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(kPlaneBlocks, n_planes), dim3(kSumThreads), 0, s,
+                                    values, plane_len, g_partial));
+  HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel, dim3(n_planes), dim3(kSumThreads), 0, s,
+                                    static_cast<const double*>(g_partial), out));
   return HB_OK;
 }
 

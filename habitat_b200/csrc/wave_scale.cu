@@ -577,6 +577,7 @@ __device__ __forceinline__ uint32_t udiv_fix_ge2(uint32_t n, uint32_t d, uint32_
 // so did the run-time destination loop against instances unrolled for a known destination count.
 __global__ void __launch_bounds__(kLutThreads, 12)
 wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
+  hb_grid_dependency_wait();
   const int D = lp.D;
   const int64_t K = lp.K;
   const int64_t k0 = (static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x) * 2;
@@ -778,9 +779,9 @@ bool try_launch_lut(const Ptrs& p, const FastParams& fp, const ClassParams& cp, 
   if (blocks > 0x7FFFFFFF || blocks < 1) return false;
   const unsigned grid = static_cast<unsigned>(blocks);
   // 12 blocks of 128 threads per SM (40 registers) measured fastest; 8, 10 and 16 were slower
-  wave_scale_lut_kernel<<<grid, kLutThreads, 0, stream>>>(p, q);
+  const cudaError_t le = hb::launch_overlapped(wave_scale_lut_kernel, dim3(grid), dim3(kLutThreads), 0, stream, p, q);
   t_path = 4;
-  const cudaError_t ce = cudaGetLastError();
+  const cudaError_t ce = le != cudaSuccess ? le : cudaGetLastError();
   *st = ce == cudaSuccess ? HB_OK : hb::cuda_fail(ce, "wave_scale_lut_kernel launch");
   return true;
 }
