@@ -337,7 +337,7 @@ def main():
                              # dram__bytes_read + dram__bytes_write of one launch (ncu capture summarised
                              # in profiles/): the 21 MB of input is read; most of the 62 MB of output is
                              # still in the 126 MB L2 when the launch ends
-                             "traffic": 29.0e6, "traffic_unit": "bytes per launch (ncu)"},
+                             "traffic": 28.3e6, "traffic_unit": "bytes per launch (ncu)"},
                 "e2e": {"value": world * pairs / (e2e_ms * 1e-3), "unit": "pairs/s",
                         "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             })
