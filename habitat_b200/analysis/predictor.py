@@ -124,12 +124,15 @@ class Predictor:
     def predict_operation(self, operation, dest_device):
         return self.predict_trace([operation], [dest_device])[0][0]
 
-    def predict_trace(self, operations, dest_devices):
+    def predict_trace(self, operations, dest_devices, cache=None):
         """Predicts every operation on every destination.
 
         Returns one list of operations per destination, in order; operations
         measured on a device of the same name as the destination are returned
-        as they are (analysis/trace.py:40-41 and operation.py:82-85)."""
+        as they are (analysis/trace.py:40-41 and operation.py:82-85).
+        `cache` is a dict the caller keeps with the operations (Trace does): the
+        flattened, GPU-resident kernel records are stored there and reused by later
+        calls with the same operations."""
         operations = list(operations)
         D = len(dest_devices)
         results = [[None] * len(operations) for _ in range(D)]
@@ -144,11 +147,11 @@ class Predictor:
                     for i in indices:
                         results[d][i] = operations[i]
             if targets:
-                self._predict_group(operations, indices, origin, dest_devices, targets, results)
+                self._predict_group(operations, indices, origin, dest_devices, targets, results, cache)
         return results
 
     # ------------------------------------------------------------------
-    def _predict_group(self, operations, indices, origin, dest_devices, targets, results):
+    def _predict_group(self, operations, indices, origin, dest_devices, targets, results, cache=None):
         dests = [dest_devices[d] for d in targets]
         wave_runs = []                     # (op index, is_backward, RunTimeMeasurement)
         mlp_ops = {op: [] for op in _MLP_OPS}
@@ -165,7 +168,7 @@ class Predictor:
                 for t, d in enumerate(targets):
                     results[d][i] = PredictedOperation(op, op.forward, op.backward, dests[t])
 
-        wave_out = self._wave_scale_runs(wave_runs, origin, dests) if wave_runs else {}
+        wave_out = self._wave_scale_runs(wave_runs, origin, dests, cache) if wave_runs else {}
         for t, d in enumerate(targets):
             fwd, bwd = {}, {}
             for (i, is_bwd, _), pred in zip(wave_runs, wave_out.get(t, [])):
@@ -182,7 +185,7 @@ class Predictor:
                     results[d][i] = PredictedOperation(
                         operations[i], RunTimePurePrediction(float(ms[t, j]), dests[t]), None, dests[t])
 
-    def _wave_scale_runs(self, wave_runs, origin, dests):
+    def _wave_scale_runs(self, wave_runs, origin, dests, cache=None):
         """-> {target index: [RunTimePrediction per run]} (predictor.py:111-130)."""
         kernels, offsets = [], [0]
         for _, _, run in wave_runs:
@@ -200,7 +203,13 @@ class Predictor:
                           for r, (_, _, run) in enumerate(wave_runs)]
             return out
         if K:
-            res = wave_batch.scale_kernels(kernels, origin, dests, self._kernel_metadata, mode)
+            key = ("flat", origin.name, mode)
+            flat = cache.get(key) if cache is not None else None
+            if flat is None or flat.count != K:
+                flat = wave_batch.FlatKernels(kernels, mode)
+                if cache is not None:
+                    cache[key] = flat
+            res = wave_batch.scale_kernels(kernels, origin, dests, self._kernel_metadata, mode, flat=flat)
             # per-run kernel-time totals on the device: [T] segment sums over the same offsets
             off = torch.from_numpy(np.asarray(offsets, np.int64)).cuda()
             sums = torch.stack([batched.segment_sum(res.scaled_ns[t], off) for t in range(T)])

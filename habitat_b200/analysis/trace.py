@@ -12,6 +12,7 @@ class Trace:
         self._device = device
         self._operations = operations
         self._run_time_ms = None
+        self._prediction_cache = {}     # flattened kernel records, filled by the first prediction
 
     @property
     def operations(self):
@@ -42,6 +43,6 @@ class Trace:
     def to_devices(self, dest_devices, predictor=None):
         """Predicted traces for several destinations from one pass over the kernels."""
         predictor = predictor if predictor is not None else self._default_predictor()
-        per_dest = predictor.predict_trace(self._operations, dest_devices)
+        per_dest = predictor.predict_trace(self._operations, dest_devices, cache=self._prediction_cache)
         return [self if dest.name == self.device.name else Trace(dest, ops)
                 for dest, ops in zip(dest_devices, per_dest)]

@@ -31,15 +31,27 @@ def flatten_kernels(kernels, mode):
     has = np.zeros(K, np.uint8)
     names = []
     for i, k in enumerate(kernels):
-        md = k.metadata
-        nb[i] = k.num_blocks
-        bs[i] = min(max(int(md["block_size"]), 0), 0xFFFF)
-        rg[i] = int(md["registers_per_thread"]) & 0xFFFF
-        smem = int(md["static_shared_memory"]) + int(md["dynamic_shared_memory"])
+        record = getattr(getattr(k, "_c", k), "launch_record", None)
+        if record is not None:
+            name, blocks, block_size, regs, smem, time_ns = record()
+        else:
+            # any object with the reference's KernelInstance surface
+            md = k.metadata
+            name, blocks, time_ns = k.name, k.num_blocks, k.run_time_ns
+            block_size, regs = int(md["block_size"]), int(md["registers_per_thread"])
+            smem = int(md["static_shared_memory"]) + int(md["dynamic_shared_memory"])
+        nb[i] = blocks
+        bs[i] = min(max(block_size, 0), 0xFFFF)
+        rg[i] = regs & 0xFFFF
         sm[i] = smem if 0 <= smem <= 0xFFFFFFFF else 0xFFFFFFFF
-        tm[i] = k.run_time_ns
-        names.append(k.name)
+        tm[i] = time_ns
+        names.append(name)
         if mode != RESIMPLIFIED:
+            if getattr(k, "_metrics_kernels", None) == [] and not k._cached_metrics:
+                # no metric records at all: the look-up below could only raise
+                if mode == ROOFLINE:
+                    raise AttributeError("Unknown metric: {}".format(_NEEDED[0].name))
+                continue
             try:
                 vals = [k.get_metric(m) for m in _NEEDED]
             except AttributeError:
@@ -57,20 +69,33 @@ def flatten_kernels(kernels, mode):
     return arrays, metrics, names
 
 
-def scale_kernels(kernels, origin_device, dest_devices, metadata_manager, mode=UNIFIED):
+class FlatKernels:
+    """The kernels of a trace flattened once and resident on the GPU: what a repeated
+    prediction of the same trace (other destinations, another strategy argument) reuses
+    instead of walking the kernel objects again."""
+
+    def __init__(self, kernels, mode):
+        arrays, metrics, self.names = flatten_kernels(kernels, mode)
+        self.mode = mode
+        self.count = len(kernels)
+        self.batch = batched.KernelBatch.from_numpy(arrays)
+        self.metrics = None
+        if metrics is not None:
+            self.metrics = batched.KernelMetricsBatch(
+                torch.from_numpy(metrics["flop_efficiency_pct"]).cuda(),
+                torch.from_numpy(metrics["dram_read_bytes"]).cuda(),
+                torch.from_numpy(metrics["dram_write_bytes"]).cuda(),
+                torch.from_numpy(metrics["has_metrics"]).cuda())
+
+
+def scale_kernels(kernels, origin_device, dest_devices, metadata_manager, mode=UNIFIED, flat=None):
     """Runs the fused kernel for `kernels` x `dest_devices`.
 
-    Returns (result, device tensors kept alive): result is a WaveResult whose
-    tensors live on the GPU; nothing is synchronised here."""
-    arrays, metrics, names = flatten_kernels(kernels, mode)
-    kb = batched.KernelBatch.from_numpy(arrays)
-    mb = None
-    if metrics is not None:
-        mb = batched.KernelMetricsBatch(
-            torch.from_numpy(metrics["flop_efficiency_pct"]).cuda(),
-            torch.from_numpy(metrics["dram_read_bytes"]).cuda(),
-            torch.from_numpy(metrics["dram_write_bytes"]).cuda(),
-            torch.from_numpy(metrics["has_metrics"]).cuda())
+    `flat` is a FlatKernels of the same kernels and mode from an earlier call (or None).
+    Returns a WaveResult whose tensors live on the GPU; nothing is synchronised here."""
+    if flat is None or flat.mode != mode or flat.count != len(kernels):
+        flat = FlatKernels(kernels, mode)
+    kb, mb, names = flat.batch, flat.metrics, flat.names
     dest_regs = None
     if metadata_manager is not None and hasattr(metadata_manager, "registers_matrix"):
         m = metadata_manager.registers_matrix(names, dest_devices)

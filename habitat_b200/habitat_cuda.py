@@ -111,6 +111,12 @@ class KernelInstance:
             dynamic_shared_memory=self._dynamic_shared_memory,
             registers_per_thread=self._registers_per_thread)
 
+    def launch_record(self):
+        """(name, num_blocks, block_size, registers_per_thread, static + dynamic shared memory,
+        run_time_ns): the fields wave scaling reads, without building the metadata dict."""
+        return (self._name, self._num_blocks, self._block_size, self._registers_per_thread,
+                self._static_shared_memory + self._dynamic_shared_memory, self._run_time_ns)
+
     def add_metric(self, name, value):
         self._metrics.append((str(name), float(value)))
 

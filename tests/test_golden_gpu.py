@@ -156,3 +156,15 @@ def test_trace_to_device(device_file, tmp_path):
     many = trace.to_devices(dests, predictor)             # all destinations in one pass
     for d, pt in enumerate(many):
         assert abs(pt.run_time_ms - g["total_ms"][d]) <= 2e-2 * g["total_ms"][d]
+    # the kernel records were flattened by the first prediction and are reused from the trace
+    from habitat_b200.analysis.wave_scaling import batch as wave_batch
+    calls = []
+    real = wave_batch.flatten_kernels
+    wave_batch.flatten_kernels = lambda *a, **k: (calls.append(1), real(*a, **k))[1]
+    try:
+        again = trace.to_devices(dests, predictor)
+    finally:
+        wave_batch.flatten_kernels = real
+    assert not calls
+    for pt, first in zip(again, many):
+        assert pt.run_time_ms == first.run_time_ms
