@@ -68,6 +68,8 @@ EXPORTS = {
         ctypes.POINTER(KernelSoA), ctypes.POINTER(KernelMetrics), ctypes.c_int64, ctypes.c_int32,
         ctypes.POINTER(ctypes.c_int32), ctypes.c_int32, ctypes.c_void_p,
         ctypes.POINTER(WaveOut), ctypes.c_void_p]),
+    "hb_device_info": (ctypes.c_int32, [ctypes.c_int32, ctypes.POINTER(DeviceSpec)]),
+    "hb_peak_flops_test": (ctypes.c_int32, [ctypes.c_int32, ctypes.POINTER(ctypes.c_double), ctypes.c_void_p]),
     "hb_wave_scale_path": (ctypes.c_int32, []),
     "hb_wave_scale_host": (ctypes.c_int32, [
         ctypes.POINTER(KernelSoA), ctypes.c_int64, ctypes.c_int32,

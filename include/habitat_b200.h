@@ -72,6 +72,20 @@ typedef struct {
  * referred to by index afterwards.  n <= HB_MAX_DEVICES.  Synchronous. */
 hb_status hb_set_devices(const hb_device_spec* rows, int32_t n);
 
+/* Fills a device-table row for CUDA device `device` from the driver's attributes: the eleven
+ * fields cpp/src/device_info.cpp:16-30 prints, the shared memory the driver reserves per block,
+ * and nominal figures for bandwidth (memory clock x bus width, double data rate), clock and
+ * single-precision peak (FMA lanes x SMs x clock) where the reference's devices.yml holds
+ * numbers from data sheets and from measure_peak_flops.py. */
+hb_status hb_device_info(int32_t device, hb_device_spec* out);
+
+/* Achieved single-precision GFLOP/s of a fused multiply-add kernel on the current device, best
+ * of `trials` launches on `stream`: a value for peak_gflops_per_second measured on the machine.
+ * Replaces cpp/src/cuda/diagnostics.cu:9-15 + tools/device-metadata/measure_peak_flops.py:10-18
+ * (which profile a kernel of dependent additions and divide by its reported efficiency).
+ * Synchronises; allocates and frees a small buffer. */
+hb_status hb_peak_flops_test(int32_t trials, double* gflops_per_second, void* stream);
+
 /* ------------------------------------------------------------------------ */
 /* Wave scaling                                                             */
 /* ------------------------------------------------------------------------ */
