@@ -87,6 +87,52 @@ _EXTRACTORS = {"conv2d": conv2d_features, "linear": linear_features, "bmm": bmm_
                "lstm": lstm_features}
 
 
+# Batched form of the extractors above for the common recording (every argument positional,
+# as torch passes them): one tuple per operation, no dictionaries.  Operations recorded with
+# keyword arguments, and the LSTM overloads, go through the named path.
+def _conv2d_row(a):
+    x, w = a[0], a[1]
+    return (x[0], x[2], x[1], w[0], w[2], _first(a[3]), _first(a[4]), 0 if a[2] is None else 1)
+
+
+def _linear_row(a):
+    x, w = a[0], a[1]
+    batch = 1
+    for v in x[:-1]:
+        batch *= v
+    return (batch, w[1], w[0], 0 if a[2] is None else 1)
+
+
+def _bmm_row(a):
+    x = a[0]
+    return (x[0], x[1], x[2], a[1][2])
+
+
+_FAST_ROWS = {
+    "conv2d": (_conv2d_row, 5, ("batch", "image_size", "in_channels", "out_channels", "kernel_size",
+                                "stride", "padding", "bias")),
+    "linear": (_linear_row, 3, ("batch", "in_features", "out_features", "bias")),
+    "bmm": (_bmm_row, 2, ("batch", "left", "middle", "right")),
+}
+
+
+def feature_matrix(name, operations, order):
+    """[n, F] float32 features of `operations` (all of kind `name`) in the column order `order`."""
+    fast = _FAST_ROWS.get(name)
+    if fast is not None:
+        row, arity, columns = fast
+        try:
+            rows = [row(op.arguments.args) if len(op.arguments.args) >= arity and not op.arguments.kwargs
+                    else None for op in operations]
+        except (TypeError, IndexError):
+            rows = [None]
+        if None not in rows:
+            m = np.array(rows, dtype=np.float32).reshape(len(rows), len(columns))
+            return np.ascontiguousarray(m[:, [columns.index(f) for f in order]])
+    extract = _EXTRACTORS[name]
+    return np.array([[extract(op)[f] for f in order] for op in operations], dtype=np.float32)
+
+
 class Predictor:
     def __init__(self, kernel_metadata_file=None, wave_scaling_strategy=unified_wave_scaling, *,
                  model_paths=None, precision="bf16"):
@@ -242,7 +288,7 @@ class Predictor:
         """-> [T, n] predicted ms (predictor.py:132-148 and the *_scale methods)."""
         pred = self._predictor(name)
         order = pred.model.features
-        feats = np.array([[_EXTRACTORS[name](op)[f] for f in order] for op in ops], dtype=np.float32)
+        feats = feature_matrix(name, ops, order)
         n, T = len(ops), len(dests)
         rows = [pred.device_row(origin.name)] + [pred.device_row(d.name) for d in dests]
         f = torch.from_numpy(np.tile(feats, (T + 1, 1))).cuda()
