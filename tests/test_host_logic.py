@@ -139,6 +139,24 @@ def test_feature_extraction():
     assert lstm_features(packed) == dict(bias=1, bidirectional=1, batch=20, seq_len=35, input_size=512,
                                          hidden_size=256, num_layers=1)
 
+    # the batched extraction (positional fast path, named fall-back) agrees with the named one
+    from habitat_b200.analysis.predictor import _EXTRACTORS, feature_matrix
+    orders = {"conv2d": ["bias", "batch", "image_size", "in_channels", "out_channels", "kernel_size",
+                         "stride", "padding"],
+              "linear": ["bias", "batch", "in_features", "out_features"],
+              "bmm": ["batch", "left", "middle", "right"],
+              "lstm": ["bias", "bidirectional", "batch", "seq_len", "input_size", "hidden_size", "num_layers"]}
+    groups = {"conv2d": [conv, conv, op("conv2d", ((1, 8, 9, 9), (16, 8, 5, 5), (16,), 1, 2, 1, 1))],
+              "linear": [lin, op("linear", ((7, 512), (10, 512), None))],
+              "bmm": [op("bmm", ((8, 10, 20), (8, 20, 30), None)), op("bmm", ((2, 3, 4), (2, 4, 5)))],
+              "lstm": [plain, packed]}
+    for name, ops in groups.items():
+        want = np.array([[_EXTRACTORS[name](o)[f] for f in orders[name]] for o in ops], np.float32)
+        assert np.array_equal(feature_matrix(name, ops, orders[name]), want), name
+    mixed = [conv, conv_kw]                      # one keyword recording sends the group down the named path
+    want = np.array([[conv2d_features(o)[f] for f in orders["conv2d"]] for o in mixed], np.float32)
+    assert np.array_equal(feature_matrix("conv2d", mixed, orders["conv2d"]), want)
+
 
 def test_runtime_predictor_checkpoints(tmp_path):
     import torch
@@ -169,21 +187,3 @@ def test_workloads_are_seeded():
     assert f.shape == (50, 7) and d.max() < 6 and f[:, 4].min() >= 32
     mu, sigma = workloads.batch_mu_sigma(f, d)
     assert mu.shape == (11,) and (sigma > 0).all()
-
-    # the batched extraction (positional fast path, named fall-back) agrees with the named one
-    from habitat_b200.analysis.predictor import _EXTRACTORS, feature_matrix
-    orders = {"conv2d": ["bias", "batch", "image_size", "in_channels", "out_channels", "kernel_size",
-                         "stride", "padding"],
-              "linear": ["bias", "batch", "in_features", "out_features"],
-              "bmm": ["batch", "left", "middle", "right"],
-              "lstm": ["bias", "bidirectional", "batch", "seq_len", "input_size", "hidden_size", "num_layers"]}
-    groups = {"conv2d": [conv, conv, op("conv2d", ((1, 8, 9, 9), (16, 8, 5, 5), (16,), 1, 2, 1, 1))],
-              "linear": [lin, op("linear", ((7, 512), (10, 512), None))],
-              "bmm": [op("bmm", ((8, 10, 20), (8, 20, 30), None)), op("bmm", ((2, 3, 4), (2, 4, 5)))],
-              "lstm": [plain, packed]}
-    for name, ops in groups.items():
-        want = np.array([[_EXTRACTORS[name](o)[f] for f in orders[name]] for o in ops], np.float32)
-        assert np.array_equal(feature_matrix(name, ops, orders[name]), want), name
-    mixed = [conv, conv_kw]                      # one keyword recording sends the group down the named path
-    want = np.array([[conv2d_features(o)[f] for f in orders["conv2d"]] for o in mixed], np.float32)
-    assert np.array_equal(feature_matrix("conv2d", mixed, orders["conv2d"]), want)
