@@ -731,7 +731,6 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
 
   if (threadIdx.x == 32) {
     for (int s = 0; s < kPairStages; ++s) {
-      // leader: own arrive.expect_tx + the peer's forwarded arrive; peer: its own only
       mbar_init(bar_full + 8 * s, 1);   // used in the leader only: its producer's arrive.expect_tx
       mbar_init(bar_empty + 8 * s, 1);
     }
