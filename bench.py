@@ -343,6 +343,32 @@ def main():
             })
             del kbs, outs, pin_in
 
+            # The same kernel on a batch eight times as large (two buffer sets, 1.3 GB): about 4 us of
+            # a launch are ramp-up and tail, so the benchmark's 21 us launches understate the rate
+            # the kernel sustains.  Reported beside the roofline figure, not instead of it.
+            if rank == 0:
+                big_k = 8 * WAVE_K
+                big = [batched.KernelBatch.from_numpy(workloads.make_kernels(big_k, 7001 + s)) for s in range(2)]
+                big_out = [batched.wave_scale(big[s], origin, bench_devs) for s in range(2)]
+                torch.cuda.synchronize()
+                g_big = torch.cuda.CUDAGraph()
+                reps = 6
+                with torch.cuda.graph(g_big, stream=stream):
+                    for i in range(reps):
+                        batched.wave_scale(big[i % 2], origin, bench_devs, out=big_out[i % 2])
+                g_big.replay()
+                b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                b0.record(stream)
+                g_big.replay()
+                b1.record(stream)
+                torch.cuda.synchronize()
+                big_ms = b0.elapsed_time(b1) / reps
+                big_gbs = big_k * WAVE_D * WAVE_BYTES_PER_PAIR / (big_ms * 1e-3) / 1e9
+                line["roofline"]["large_batch"] = {
+                    "kernels": big_k, "us_per_launch": big_ms * 1e3, "achieved": big_gbs,
+                    "frac": big_gbs / peaks["hbm_gbs"]}
+                del big, big_out, g_big
+
         # ------------------------------ MLP predictor ------------------------------
         if args.only in ("both", "mlp"):
             w = workloads.torch_init_mlp_weights(MLP_OP)
