@@ -302,7 +302,9 @@ def main():
             # pipeline of the package (upload + kernel of step i + 1 overlap the download of step i)
             e2e_steps = max(4, min(steps, 12))
             pin_in = [pinned_inputs(torch, h) for h in host_sets[:2]]
-            pipe = hostio.WaveScaleHost(origin, bench_devs, WAVE_K, depth=2)
+            # the step's result on the host: the predicted times [6 x K] (what Predictor._wave_scale
+            # returns per kernel); occupancies and wave counts stay on the device
+            pipe = hostio.WaveScaleHost(origin, bench_devs, WAVE_K, depth=2, results=("scaled_ns",))
             h2d, d2h = pipe.h2d_bytes, pipe.d2h_bytes
             for i in range(2):
                 pipe.submit(pin_in[i % 2], i % 2)
@@ -328,6 +330,8 @@ def main():
                                  "the 126 MB L2" % (WAVE_SETS, WAVE_SETS * pairs * WAVE_BYTES_PER_PAIR / 1e6),
                            "launch": "the timed steps are replayed from one CUDA graph; a step is the "
                                      "wave-scale kernel plus the per-destination totals",
+                           "e2e": "pinned host records in (20 B per kernel), predicted times out (4 B per pair), "
+                                  "three streams, two batches in flight",
                            "collective": "one all-reduce of the [steps x 6] totals" if world > 1 else "none"},
                 "roofline": {"bound": "hbm", "kernel": wave_kernel,
                              "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",

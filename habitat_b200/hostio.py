@@ -42,8 +42,14 @@ class WaveScaleHost(_TwoStreams):
     of the batch appear in self.host_out[slot] (pinned tensors, same names as
     batched.WaveResult)."""
 
-    def __init__(self, origin, dests: Sequence, K: int, depth: int = 2):
+    def __init__(self, origin, dests: Sequence, K: int, depth: int = 2, results: Sequence[str] = _WAVE_OUT):
+        """results: which outputs are copied back to the host (names of batched.WaveResult).  The
+        predicted times are what the analyzer's path returns per kernel; occupancies and wave
+        counts stay on the device (self.dev_out[slot]) unless they are listed."""
         super().__init__(depth)
+        unknown = [r for r in results if r not in _WAVE_OUT]
+        if unknown:
+            raise ValueError("unknown wave-scaling outputs: %s" % unknown)
         self.origin, self.dests, self.K = origin, list(dests), K
         D = len(self.dests)
         dt = dict(num_blocks=torch.int32, block_size=torch.int16, regs_per_thread=torch.int16,
@@ -58,7 +64,7 @@ class WaveScaleHost(_TwoStreams):
                 dest_waves=torch.empty((D, K), dtype=torch.uint32, device="cuda"),
                 origin_occupancy=torch.empty((K,), dtype=torch.uint8, device="cuda"),
                 origin_waves=torch.empty((K,), dtype=torch.uint32, device="cuda")))
-        self.host_out = [{k: torch.empty_like(getattr(o, k), device="cpu").pin_memory() for k in _WAVE_OUT}
+        self.host_out = [{k: torch.empty_like(getattr(o, k), device="cpu").pin_memory() for k in results}
                          for o in self.dev_out]
         self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.dev_in[0].values())
         self.d2h_bytes = sum(t.numel() * t.element_size() for t in self.host_out[0].values())

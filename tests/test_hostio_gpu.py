@@ -42,6 +42,19 @@ def test_wave_scale_pipeline(bench_devices):
             assert err.max() <= 1e-6
     assert pipe.h2d_bytes == 20 * K and pipe.d2h_bytes == (9 * 6 + 5) * K
 
+    # only the predicted times copied back; the other outputs stay on the device
+    times = hostio.WaveScaleHost(bench_devices[0], bench_devices, K, depth=2, results=("scaled_ns",))
+    times.submit(_pinned(batches[0]), 0)
+    times.wait(0)
+    ref = run_wave_oracle(batches[0], bench_devices[0], bench_devices)
+    ok = ref["status"] <= 1
+    got = to_numpy(times.host_out[0]["scaled_ns"])
+    assert list(times.host_out[0]) == ["scaled_ns"] and times.d2h_bytes == 4 * 6 * K
+    assert np.isnan(got[~ok]).all() and (np.abs(got[ok] - ref["scaled_ns"][ok]) <= 1e-6 * ref["scaled_ns"][ok]).all()
+    assert np.array_equal(to_numpy(times.dev_out[0].dest_occupancy), ref["dest_occupancy"])
+    with pytest.raises(ValueError):
+        hostio.WaveScaleHost(bench_devices[0], bench_devices, K, results=("scaled",))
+
 
 def test_mlp_pipeline():
     op, Q = "linear", 5000
