@@ -129,3 +129,20 @@ def test_repeatable(precision, Q):
     torch.cuda.synchronize()
     h.check_status()
     h.close()
+
+
+@pytest.mark.parametrize("precision", ["bf16", "bf16x3"])
+@pytest.mark.parametrize("layers", [1, 2, 3, 5])
+def test_layer_by_layer(layers, precision):
+    """The fused chain does not expose its activations, so each depth is checked instead: the same
+    stack cut after 1, 2, 3, 5 hidden layers (own fc2 each) at 129 queries - one full tile plus one
+    query - with weights that keep the activations input-dependent.  A layer that went wrong shows
+    at its depth and not only in the full eight-layer result."""
+    w = workloads.init_mlp_weights("bmm", seed=40 + layers, layers=layers, gain=np.sqrt(6.0))
+    got, ref32, ref64 = _run("bmm", 129, w, precision, seed=1005)
+    spread = ref64.std()
+    err = np.abs(got - ref64)
+    if precision == "bf16":
+        assert err.max() <= 8e-2 * spread + 2e-2 * np.abs(ref64).max()
+    else:
+        assert err.max() <= 2e-4 * (spread + np.abs(ref64).max())
