@@ -980,13 +980,27 @@ extern "C" hb_status hb_set_devices(const hb_device_spec* rows, int32_t n) {
   for (int i = 0; i < kMagicN; ++i) magic[i] = magic_of(static_cast<uint32_t>(i));
   HB_CUDA_TRY(cudaMemcpyToSymbol(g_magic, magic, sizeof(magic)));
   {
-    std::vector<uint8_t> r(static_cast<size_t>(n) * kLutW * kLutU), w(static_cast<size_t>(n) * kLutWPad),
-        sm(static_cast<size_t>(n) * kLutS);
+    // Host copies of the tables persist between calls: a row is tabulated again only when its
+    // specification changed (callers append rows one at a time and upload the whole table).
+    static std::vector<uint8_t> r(static_cast<size_t>(HB_MAX_DEVICES) * kLutW * kLutU),
+        w(static_cast<size_t>(HB_MAX_DEVICES) * kLutWPad), sm(static_cast<size_t>(HB_MAX_DEVICES) * kLutS);
+    static hb_device_spec built[HB_MAX_DEVICES];
+    static bool have[HB_MAX_DEVICES] = {};
     for (int i = 0; i < n; ++i) {
+      if (have[i] && std::memcmp(&built[i], &g_rows[i], sizeof(hb_device_spec)) == 0) continue;
+      built[i] = g_rows[i];
+      have[i] = true;
       g_lut_ok[i] = lut_row_ok(g_rows[i], g_pre[i]);
-      if (g_lut_ok[i])
-        build_row_lut(fold_fast(g_rows[i], g_pre[i]), &r[static_cast<size_t>(i) * kLutW * kLutU],
-                      &w[static_cast<size_t>(i) * kLutWPad], &sm[static_cast<size_t>(i) * kLutS], magic);
+      uint8_t* ri = &r[static_cast<size_t>(i) * kLutW * kLutU];
+      uint8_t* wi = &w[static_cast<size_t>(i) * kLutWPad];
+      uint8_t* si = &sm[static_cast<size_t>(i) * kLutS];
+      if (g_lut_ok[i]) {
+        build_row_lut(fold_fast(g_rows[i], g_pre[i]), ri, wi, si, magic);
+      } else {
+        std::memset(ri, 0, kLutW * kLutU);
+        std::memset(wi, 0, kLutWPad);
+        std::memset(si, 0, kLutS);
+      }
     }
     float2 lp2[33];
     for (int i = 0; i < 33; ++i) {
@@ -997,9 +1011,9 @@ extern "C" hb_status hb_set_devices(const hb_device_spec* rows, int32_t n) {
     std::vector<uint32_t> wm(kWaveMagicN);
     for (int i = 0; i < kWaveMagicN; ++i) wm[i] = magic_of(static_cast<uint32_t>(i));
     HB_CUDA_TRY(cudaMemcpyToSymbol(g_wave_magic, wm.data(), wm.size() * sizeof(uint32_t)));
-    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_r, r.data(), r.size()));
-    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_w, w.data(), w.size()));
-    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_s, sm.data(), sm.size()));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_r, r.data(), static_cast<size_t>(n) * kLutW * kLutU));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_w, w.data(), static_cast<size_t>(n) * kLutWPad));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_s, sm.data(), static_cast<size_t>(n) * kLutS));
   }
   return HB_OK;
 }
