@@ -269,9 +269,24 @@ def main():
                 wave_step(i)
             torch.cuda.synchronize()
             g_full, g_kernel = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            # Timed steps: the totals of step i run on a second stream beside the wave kernel of
+            # step i + 1 (a buffer set is reused only after its totals were taken).
+            side = torch.cuda.Stream()
             with torch.cuda.graph(g_full, stream=stream):
+                waved = [torch.cuda.Event() for _ in range(steps)]
+                summed = [torch.cuda.Event() for _ in range(steps)]
+                side.wait_stream(stream)
                 for i in range(steps):
-                    wave_step(i)
+                    s = i % WAVE_SETS
+                    if i >= WAVE_SETS:
+                        stream.wait_event(summed[i - WAVE_SETS])
+                    batched.wave_scale(kbs[s], origin, bench_devs, out=outs[s])
+                    waved[i].record(stream)
+                    with torch.cuda.stream(side):
+                        side.wait_event(waved[i])
+                        batched.plane_sum(outs[s].scaled_ns, out=totals[i % steps])
+                        summed[i].record(side)
+                stream.wait_stream(side)
             with torch.cuda.graph(g_kernel, stream=stream):
                 for i in range(steps):
                     wave_step(i, with_sum=False)
@@ -329,7 +344,8 @@ def main():
                            "l2": "%d rotating buffer sets (%.0f MB) so that no step finds its data in "
                                  "the 126 MB L2" % (WAVE_SETS, WAVE_SETS * pairs * WAVE_BYTES_PER_PAIR / 1e6),
                            "launch": "the timed steps are replayed from one CUDA graph; a step is the "
-                                     "wave-scale kernel plus the per-destination totals",
+                                     "wave-scale kernel plus the per-destination totals, the totals of "
+                                     "step i on a second stream beside the kernel of step i + 1",
                            "e2e": "pinned host records in (20 B per kernel), predicted times out (4 B per pair), "
                                   "three streams, two batches in flight",
                            "collective": "one all-reduce of the [steps x 6] totals" if world > 1 else "none"},
