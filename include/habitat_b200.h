@@ -253,7 +253,10 @@ hb_status hb_segment_sum(const float* values, const int64_t* offsets, int64_t n_
 
 /* Sum of each of n_planes contiguous planes of plane_len float32 values,
  * skipping NaN entries (pairs the reference would have raised on); used for
- * per-destination totals of hb_wave_out.scaled_ns.  out [n_planes] float64. */
+ * per-destination totals of hb_wave_out.scaled_ns.  out [n_planes] float64.
+ * The partial sums of all calls share one scratch buffer of the library (allocated, and
+ * grown, on the first call that needs it - a set-up step): calls on one device must be
+ * ordered, on one stream or by events. */
 hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_t n_planes, double* out,
                        void* stream);
 
