@@ -146,3 +146,19 @@ def test_layer_by_layer(layers, precision):
         assert err.max() <= 8e-2 * spread + 2e-2 * np.abs(ref64).max()
     else:
         assert err.max() <= 2e-4 * (spread + np.abs(ref64).max())
+
+
+def test_empty_and_single_query():
+    w = workloads.torch_init_mlp_weights("linear")
+    feats, dev = workloads.make_queries("linear", 16, 3)
+    mu, sigma = workloads.batch_mu_sigma(feats, dev)
+    for precision in ("bf16", "bf16x3"):
+        h = batched.MLPHandle(4, mu=mu, sigma=sigma, device_features=DEVF, precision=precision, **w)
+        none = h.predict(torch.from_numpy(feats[:0]).cuda(), torch.from_numpy(dev[:0]).cuda())
+        one = h.predict(torch.from_numpy(feats[:1]).cuda(), torch.from_numpy(dev[:1]).cuda())
+        torch.cuda.synchronize()
+        h.check_status()
+        assert none.shape == (0,) and one.shape == (1,)
+        ref = omlp.predict(w, feats[:1], dev[:1], DEVF, mu, sigma, np.float32)
+        assert abs(float(one[0]) - ref[0]) <= 2e-2 * abs(ref[0])
+        h.close()

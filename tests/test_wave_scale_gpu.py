@@ -200,3 +200,15 @@ def test_tabulated_kernel_on_edges(bench_devices, device_file):
         taken += got["fast_path"] == "wave_scale_lut_kernel"
         assert_wave_equal(got, run_wave_oracle(kernels, devs[0], devs))
     assert taken >= 2
+
+
+@pytest.mark.parametrize("D", [33, 64])
+def test_many_destinations(device_file, D):
+    """More than 32 destinations per call take the generic kernel (the faster ones hold at most 32
+    rows in their parameters); same results."""
+    names = sorted(device_file)
+    dests = [device_file[names[i % len(names)]] for i in range(D)]
+    kernels = workloads.make_kernels(2000, seed=5)
+    got = run_wave_gpu(kernels, device_file["V100"], dests)
+    assert got["fast_path"] == "wave_scale_kernel"
+    assert_wave_equal(got, run_wave_oracle(kernels, device_file["V100"], dests))
