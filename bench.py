@@ -188,8 +188,10 @@ def run_reference(args):
         "unit": "pairs/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * wall / steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "i32+f64", "data": "synthetic",
-        "config": {"workload": "wave scaling, config-2 distribution, 6 destination rows; each step a "
-                               "bounded sample on the host cores"},
+        "config": {"workload": "config 2: wave scaling of 1,048,576 synthetic kernels from a "
+                               "V100-class origin to 6 device rows, per GPU and step",
+                   "sample": "each step a bounded sample of that workload (same distribution, same six "
+                             "rows) on the host cores"},
         "cpu_baseline": wave,
         "e2e": {"value": wave["value"], "unit": "pairs/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
