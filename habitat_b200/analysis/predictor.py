@@ -265,13 +265,22 @@ class Predictor:
         else:
             scaled = np.zeros((T, 0), np.float32)
             sums = np.zeros((T, n_runs))
+        # per-run overhead (predictor.py:113-116 of the reference) does not depend on the destination
+        overheads = []
+        for _, _, run in wave_runs:
+            overhead_ns = ms_to_ns(run.run_time_ms) - sum(k.run_time_ns for k in run.kernels)
+            overheads.append(0 if overhead_ns < 0 else overhead_ns)
         out = {}
         for t, dest in enumerate(dests):
+            times = scaled[t].tolist()          # one conversion per destination, not one per kernel
+            totals = sums[t].tolist()
             runs = []
-            for r, (_, _, run) in enumerate(wave_runs):
+            for r in range(n_runs):
                 lo, hi = offsets[r], offsets[r + 1]
-                preds = [PredictedKernel(k, float(ns)) for k, ns in zip(kernels[lo:hi], scaled[t, lo:hi])]
-                runs.append(self._make_run(run, preds, dest, float(sums[t, r])))
+                preds = [PredictedKernel(kernels[i], times[i]) for i in range(lo, hi)]
+                pred = RunTimePrediction(overhead_ns=overheads[r], predicted_kernels=preds, device=dest)
+                pred._run_time_ms = ns_to_ms(overheads[r] + totals[r])
+                runs.append(pred)
             out[t] = runs
         return out
 
