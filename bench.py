@@ -471,6 +471,31 @@ def main():
                         "h2d_bytes_per_step": int(mpipe.h2d_bytes),
                         "d2h_bytes_per_step": int(mpipe.d2h_bytes)},
             }
+            if rank == 0:
+                # config 1 beside it: the linear predictor on 65,536 queries in the split-precision mode
+                # (the 1e-4 configuration), kernel time only
+                w1 = workloads.torch_init_mlp_weights("linear")
+                f1, r1 = workloads.make_queries("linear", 65536, 1001)
+                mu1, sigma1 = workloads.batch_mu_sigma(f1, r1)
+                h1 = batched.MLPHandle(f1.shape[1], mu=mu1, sigma=sigma1, precision="bf16x3",
+                                       device_features=workloads.BENCH_DEVICE_FEATURES, **w1)
+                d_f1, d_r1 = torch.from_numpy(f1).cuda(), torch.from_numpy(r1).cuda()
+                d_o1 = torch.empty((65536,), dtype=torch.float32, device="cuda")
+                for _ in range(3):
+                    h1.predict(d_f1, d_r1, out=d_o1)
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                c0.record(stream)
+                for _ in range(5):
+                    h1.predict(d_f1, d_r1, out=d_o1)
+                c1.record(stream)
+                torch.cuda.synchronize()
+                h1.check_status()
+                ms1 = c0.elapsed_time(c1) / 5
+                mlp["split_precision"] = {
+                    "workload": "config 1: linear predictor, 65,536 queries, bf16 hi + lo operands (three "
+                                "products per step), tolerance 1e-4",
+                    "ms_per_launch": ms1, "value": 65536 / (ms1 * 1e-3), "unit": "predictions/s"}
+                h1.close()
             if "metric" in line:
                 line["mlp"] = mlp
             else:
