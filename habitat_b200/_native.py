@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "_lib", "libhabitat_b200.so")
+# HABITAT_B200_LIB selects another build of the same library (the index-checked one, for tests)
+LIB_PATH = os.environ.get("HABITAT_B200_LIB") or os.path.join(_PKG_DIR, "_lib", "libhabitat_b200.so")
 
 HB_OK = 0
 HB_ERR_INVALID_ARGUMENT = 1
@@ -100,6 +101,11 @@ EXPORTS = {
         ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
     "hb_plane_sum_static": (ctypes.c_int32, [
         ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "hb_plane_sum_scratch_planes": (ctypes.c_int64, [ctypes.c_int32]),
+    "hb_group_sum": (ctypes.c_int32, [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "hb_mlp_inject_status": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_int32]),
+    "hb_bounds_check_word": (ctypes.c_int32, [ctypes.POINTER(ctypes.c_uint32), ctypes.c_int32]),
 }
 
 _lib = None

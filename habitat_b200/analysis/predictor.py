@@ -7,6 +7,7 @@ operation, a trace is flattened once and goes through three device launches
 (wave scaling, the fused MLP chain per operation kind, the ratio/clamp), for
 any number of destination devices at a time (predict_trace).
 """
+import collections.abc
 import functools
 import logging
 import operator
@@ -25,7 +26,7 @@ from habitat_b200.analysis.wave_scaling import batch as wave_batch
 from habitat_b200.analysis.wave_scaling.metadata import MetadataManager
 from habitat_b200.analysis.wave_scaling.unified import unified_wave_scaling
 from habitat_b200.data import path_to_data
-from habitat_b200.utils import ms_to_ns, name_all_arguments, ns_to_ms
+from habitat_b200.utils import name_all_arguments
 
 logger = logging.getLogger(__name__)
 
@@ -133,6 +134,133 @@ def feature_matrix(name, operations, order):
     return np.array([[extract(op)[f] for f in order] for op in operations], dtype=np.float32)
 
 
+class _LazyRunTimePrediction(RunTimePrediction):
+    """A predicted pass whose time is known (summed on the device) and whose
+    PredictedKernel objects are only built when somebody asks for them."""
+
+    def __init__(self, overhead_ns, measured_kernels, times_ns, total_kernel_ns, device):
+        super().__init__(overhead_ns=overhead_ns, predicted_kernels=None, device=device)
+        self._measured_kernels = measured_kernels
+        self._times_ns = times_ns
+        self._run_time_ms = (overhead_ns + total_kernel_ns) / 1e6
+
+    @property
+    def kernels(self):
+        if self._predicted_kernels is None:
+            self._predicted_kernels = [PredictedKernel(k, float(t))
+                                       for k, t in zip(self._measured_kernels, self._times_ns)]
+        return self._predicted_kernels
+
+
+class _GroupPlan:
+    """Everything about the operations of one origin device that does not depend on the
+    destination: which operation is predicted how, the flattened kernels of the wave-scaled
+    passes, launch overheads, MLP feature matrices.  Built by the first prediction of a trace
+    and kept with it."""
+
+    def __init__(self, operations, indices, mode):
+        self.indices = np.asarray(indices, np.int64)
+        self.mode = mode
+        wave_idx, fwd_run, bwd_run, runs = [], [], [], []
+        self.mlp_idx = {op: [] for op in _MLP_OPS}
+        self.passthrough_idx = []
+        for i in indices:
+            op = operations[i]
+            name = op.name
+            if name not in SPECIAL_OPERATIONS:
+                wave_idx.append(i)
+                fwd_run.append(len(runs))
+                runs.append(op.forward)
+                if op.backward is not None:
+                    bwd_run.append(len(runs))
+                    runs.append(op.backward)
+                else:
+                    bwd_run.append(-1)
+            elif name in self.mlp_idx:
+                self.mlp_idx[name].append(i)
+            else:
+                logger.warning("Unhandled special operation: %s", name)
+                self.passthrough_idx.append(i)
+        self.wave_idx = np.asarray(wave_idx, np.int64)
+        self.fwd_run = np.asarray(fwd_run, np.int64)
+        self.bwd_run = np.asarray(bwd_run, np.int64)
+        self.runs = runs
+        self.kernels = []
+        offsets = [0]
+        for run in runs:
+            self.kernels.extend(run.kernels)
+            offsets.append(len(self.kernels))
+        self.offsets = np.asarray(offsets, np.int64)
+        self.flat = wave_batch.FlatKernels(self.kernels, mode) if (self.kernels and mode is not None) else None
+        # launch overhead of a pass (predictor.py:113-116 of the reference): wall time minus kernel time
+        measured = np.array([k.run_time_ns for k in self.kernels], np.float64)
+        per_run = np.add.reduceat(np.concatenate([measured, [0.0]]), self.offsets[:-1]) if runs else np.zeros(0)
+        per_run = np.where(self.offsets[1:] > self.offsets[:-1], per_run, 0.0) if runs else per_run
+        wall_ns = np.array([run.run_time_ms for run in runs], np.float64) * 1e6
+        self.overheads = np.maximum(wall_ns - per_run, 0.0)
+        self.offsets_dev = None
+        self.mlp_inputs = {}      # op kind -> (feature matrix, measured ms), filled on first use
+
+
+class PredictedOperations(collections.abc.Sequence):
+    """The operations of a trace as predicted for one destination.  Behaves like the list the
+    reference builds (len, indexing, iteration); PredictedOperation, RunTimePrediction and
+    PredictedKernel objects are created when an element is first touched, the per-operation
+    times (`run_times_ms`) and their sum (`total_run_time_ms`) are there from the start."""
+
+    def __init__(self, operations, dest):
+        self._operations = operations
+        self._dest = dest
+        n = len(operations)
+        self._made = [None] * n
+        self._kind = np.zeros(n, np.int8)       # 0 as measured, 1 wave-scaled, 2 MLP, 3 special passed through
+        self._group = np.zeros(n, np.int32)
+        self._a = np.full(n, -1, np.int64)      # wave: forward run; MLP: position in the group's ms array
+        self._b = np.full(n, -1, np.int64)      # wave: backward run or -1
+        self._groups = []                       # per origin group: dict(plan, times, totals, ms)
+        self.run_times_ms = np.zeros(n, np.float64)
+        self._total = None
+
+    def __len__(self):
+        return len(self._operations)
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return [self[j] for j in range(*i.indices(len(self)))]
+        if i < 0:
+            i += len(self)
+        made = self._made[i]
+        if made is None:
+            made = self._made[i] = self._make(i)
+        return made
+
+    @property
+    def total_run_time_ms(self):
+        if self._total is None:
+            self._total = float(self.run_times_ms.sum())
+        return self._total
+
+    def _make(self, i):
+        op = self._operations[i]
+        kind = self._kind[i]
+        if kind == 0:
+            return op
+        if kind == 3:
+            return PredictedOperation(op, op.forward, op.backward, self._dest)
+        g = self._groups[self._group[i]]
+        if kind == 2:
+            return PredictedOperation(op, RunTimePurePrediction(float(self.run_times_ms[i]), self._dest),
+                                      None, self._dest)
+        plan = g["plan"]
+
+        def run(r):
+            lo, hi = plan.offsets[r], plan.offsets[r + 1]
+            return _LazyRunTimePrediction(float(plan.overheads[r]), plan.kernels[lo:hi], g["times"][lo:hi],
+                                          float(g["totals"][r]), self._dest)
+        b = self._b[i]
+        return PredictedOperation(op, run(self._a[i]), run(b) if b >= 0 else None, self._dest)
+
+
 class Predictor:
     def __init__(self, kernel_metadata_file=None, wave_scaling_strategy=unified_wave_scaling, *,
                  model_paths=None, precision="bf16"):
@@ -173,25 +301,32 @@ class Predictor:
     def predict_trace(self, operations, dest_devices, cache=None):
         """Predicts every operation on every destination.
 
-        Returns one list of operations per destination, in order; operations
-        measured on a device of the same name as the destination are returned
-        as they are (analysis/trace.py:40-41 and operation.py:82-85).
-        `cache` is a dict the caller keeps with the operations (Trace does): the
-        flattened, GPU-resident kernel records are stored there and reused by later
-        calls with the same operations."""
-        operations = list(operations)
+        Returns one sequence of operations per destination, in order (PredictedOperations:
+        list-like, elements built on first access); operations measured on a device of the
+        same name as the destination are returned as they are (analysis/trace.py:40-41 and
+        operation.py:82-85).  `cache` is a dict the caller keeps with the operations (Trace
+        does): the destination-independent plan of the trace (flattened, GPU-resident kernel
+        records, overheads, MLP features) is stored there and reused by later calls."""
+        if not isinstance(operations, (list, tuple)):
+            operations = list(operations)
         D = len(dest_devices)
-        results = [[None] * len(operations) for _ in range(D)]
-        by_origin = {}
-        for i, op in enumerate(operations):
-            by_origin.setdefault(op.device.name, []).append(i)
-        for indices in by_origin.values():
+        results = [PredictedOperations(operations, dest) for dest in dest_devices]
+        key = ("origins", len(operations))
+        by_origin = cache.get(key) if cache is not None else None
+        if by_origin is None:
+            by_origin = {}
+            for i, op in enumerate(operations):
+                by_origin.setdefault(op.device.name, []).append(i)
+            if cache is not None:
+                cache[key] = by_origin
+        for origin_name, indices in by_origin.items():
             origin = operations[indices[0]].device
-            targets = [d for d in range(D) if dest_devices[d].name != origin.name]
-            for d in range(D):
-                if d not in targets:
-                    for i in indices:
-                        results[d][i] = operations[i]
+            targets = [d for d in range(D) if dest_devices[d].name != origin_name]
+            same = [d for d in range(D) if dest_devices[d].name == origin_name]
+            if same:
+                ms = np.array([operations[i].run_time_ms for i in indices], np.float64)
+                for d in same:
+                    results[d].run_times_ms[indices] = ms      # kind 0: the measured operation itself
             if targets:
                 self._predict_group(operations, indices, origin, dest_devices, targets, results, cache)
         return results
@@ -199,118 +334,89 @@ class Predictor:
     # ------------------------------------------------------------------
     def _predict_group(self, operations, indices, origin, dest_devices, targets, results, cache=None):
         dests = [dest_devices[d] for d in targets]
-        wave_runs = []                     # (op index, is_backward, RunTimeMeasurement)
-        mlp_ops = {op: [] for op in _MLP_OPS}
-        for i in indices:
-            op = operations[i]
-            if op.name not in SPECIAL_OPERATIONS:
-                wave_runs.append((i, False, op.forward))
-                if op.backward is not None:
-                    wave_runs.append((i, True, op.backward))
-            elif op.name in _MLP_OPS:
-                mlp_ops[op.name].append(i)
-            else:
-                logger.warning("Unhandled special operation: %s", op.name)
-                for t, d in enumerate(targets):
-                    results[d][i] = PredictedOperation(op, op.forward, op.backward, dests[t])
-
-        wave_out = self._wave_scale_runs(wave_runs, origin, dests, cache) if wave_runs else {}
+        mode = getattr(self._wave_scaling_strategy, "batch_mode", None)
+        key = ("plan", origin.name, mode, len(indices))
+        plan = cache.get(key) if cache is not None else None
+        if plan is None:
+            plan = _GroupPlan(operations, indices, mode)
+            if cache is not None:
+                cache[key] = plan
+        T = len(dests)
+        times, totals = self._wave_scale_plan(plan, origin, dests)
+        run_ms = (plan.overheads[None, :] + totals) / 1e6                    # [T, runs]
         for t, d in enumerate(targets):
-            fwd, bwd = {}, {}
-            for (i, is_bwd, _), pred in zip(wave_runs, wave_out.get(t, [])):
-                (bwd if is_bwd else fwd)[i] = pred
-            for i, pred in fwd.items():
-                results[d][i] = PredictedOperation(operations[i], pred, bwd.get(i), dests[t])
-
-        for name, idx in mlp_ops.items():
+            res = results[d]
+            g = len(res._groups)
+            res._groups.append(dict(plan=plan, times=times[t], totals=totals[t]))
+            if len(plan.wave_idx):
+                res._kind[plan.wave_idx] = 1
+                res._group[plan.wave_idx] = g
+                res._a[plan.wave_idx] = plan.fwd_run
+                res._b[plan.wave_idx] = plan.bwd_run
+                ms = run_ms[t][plan.fwd_run]
+                has_bwd = plan.bwd_run >= 0
+                ms = ms + np.where(has_bwd, run_ms[t][np.maximum(plan.bwd_run, 0)], 0.0)
+                res.run_times_ms[plan.wave_idx] = ms
+            for i in plan.passthrough_idx:
+                res._kind[i] = 3
+                res.run_times_ms[i] = operations[i].run_time_ms
+        for name, idx in plan.mlp_idx.items():
             if not idx:
                 continue
-            ms = self._special_scale_ops(name, [operations[i] for i in idx], origin, dests)
+            ms = self._special_scale_ops(name, [operations[i] for i in idx], origin, dests, plan)
+            idx = np.asarray(idx, np.int64)
             for t, d in enumerate(targets):
-                for j, i in enumerate(idx):
-                    results[d][i] = PredictedOperation(
-                        operations[i], RunTimePurePrediction(float(ms[t, j]), dests[t]), None, dests[t])
+                res = results[d]
+                res._kind[idx] = 2
+                res.run_times_ms[idx] = ms[t]
 
-    def _wave_scale_runs(self, wave_runs, origin, dests, cache=None):
-        """-> {target index: [RunTimePrediction per run]} (predictor.py:111-130)."""
-        kernels, offsets = [], [0]
-        for _, _, run in wave_runs:
-            kernels.extend(run.kernels)
-            offsets.append(len(kernels))
-        n_runs, K, T = len(wave_runs), len(kernels), len(dests)
-        mode = getattr(self._wave_scaling_strategy, "batch_mode", None)
-        if mode is None:
+    def _wave_scale_plan(self, plan, origin, dests):
+        """-> (scaled kernel times [T, K], per-pass kernel totals [T, runs]) on the host, float64
+        (predictor.py:111-130 of the reference for every pass and destination at once)."""
+        T, K, n_runs = len(dests), len(plan.kernels), len(plan.runs)
+        if plan.mode is None:
             # a user-supplied strategy: the reference's per-kernel protocol
-            out = {}
-            for t, dest in enumerate(dests):
-                preds = [self._wave_scaling_strategy(k, origin, dest, self._kernel_metadata)
-                         for k in kernels]
-                out[t] = [self._make_run(run, preds[offsets[r]:offsets[r + 1]], dest, None)
-                          for r, (_, _, run) in enumerate(wave_runs)]
-            return out
-        if K:
-            key = ("flat", origin.name, mode)
-            flat = cache.get(key) if cache is not None else None
-            if flat is None or flat.count != K:
-                flat = wave_batch.FlatKernels(kernels, mode)
-                if cache is not None:
-                    cache[key] = flat
-            res = wave_batch.scale_kernels(kernels, origin, dests, self._kernel_metadata, mode, flat=flat)
-            # per-run kernel-time totals on the device: [T] segment sums over the same offsets
-            off = torch.from_numpy(np.asarray(offsets, np.int64)).cuda()
-            sums = torch.stack([batched.segment_sum(res.scaled_ns[t], off) for t in range(T)])
-            scaled = res.scaled_ns.cpu().numpy()
-            wave_batch.raise_like_reference(res.status.cpu().numpy())
-            sums = sums.cpu().numpy()
-        else:
-            scaled = np.zeros((T, 0), np.float32)
-            sums = np.zeros((T, n_runs))
-        # per-run overhead (predictor.py:113-116 of the reference) does not depend on the destination
-        overheads = []
-        for _, _, run in wave_runs:
-            overhead_ns = ms_to_ns(run.run_time_ms) - sum(k.run_time_ns for k in run.kernels)
-            overheads.append(0 if overhead_ns < 0 else overhead_ns)
-        out = {}
-        for t, dest in enumerate(dests):
-            times = scaled[t].tolist()          # one conversion per destination, not one per kernel
-            totals = sums[t].tolist()
-            runs = []
+            times = np.array([[self._wave_scaling_strategy(k, origin, dest, self._kernel_metadata).run_time_ns
+                               for k in plan.kernels] for dest in dests], np.float64).reshape(T, K)
+            totals = np.zeros((T, n_runs))
             for r in range(n_runs):
-                lo, hi = offsets[r], offsets[r + 1]
-                preds = [PredictedKernel(kernels[i], times[i]) for i in range(lo, hi)]
-                pred = RunTimePrediction(overhead_ns=overheads[r], predicted_kernels=preds, device=dest)
-                pred._run_time_ms = ns_to_ms(overheads[r] + totals[r])
-                runs.append(pred)
-            out[t] = runs
-        return out
+                totals[:, r] = times[:, plan.offsets[r]:plan.offsets[r + 1]].sum(axis=1)
+            return times, totals
+        if K == 0:
+            return np.zeros((T, 0)), np.zeros((T, n_runs))
+        res = wave_batch.scale_kernels(plan.kernels, origin, dests, self._kernel_metadata, plan.mode,
+                                       flat=plan.flat)
+        if plan.offsets_dev is None:
+            plan.offsets_dev = torch.from_numpy(plan.offsets).cuda()
+        # per-pass kernel-time totals on the device: segment sums over the same offsets
+        sums = torch.stack([batched.segment_sum(res.scaled_ns[t], plan.offsets_dev) for t in range(T)])
+        scaled = res.scaled_ns.cpu().numpy()
+        wave_batch.raise_like_reference(scaled)
+        return scaled, sums.cpu().numpy()
 
-    @staticmethod
-    def _make_run(run, predicted_kernels, dest, kernel_total_ns):
-        overhead_ns = ms_to_ns(run.run_time_ms) - sum(k.run_time_ns for k in run.kernels)
-        pred = RunTimePrediction(overhead_ns=0 if overhead_ns < 0 else overhead_ns,
-                                 predicted_kernels=predicted_kernels, device=dest)
-        if kernel_total_ns is not None:
-            pred._run_time_ms = ns_to_ms(pred._overhead_ns + kernel_total_ns)
-        return pred
-
-    def _special_scale_ops(self, name, ops, origin, dests):
+    def _special_scale_ops(self, name, ops, origin, dests, plan=None):
         """-> [T, n] predicted ms (predictor.py:132-148 and the *_scale methods)."""
         pred = self._predictor(name)
         order = pred.model.features
-        feats = feature_matrix(name, ops, order)
+        cached = plan.mlp_inputs.get(name) if plan is not None else None
+        if cached is None:
+            cached = (feature_matrix(name, ops, order), np.array([op.run_time_ms for op in ops], np.float32))
+            if plan is not None:
+                plan.mlp_inputs[name] = cached
+        feats, rt_host = cached
         n, T = len(ops), len(dests)
         rows = [pred.device_row(origin.name)] + [pred.device_row(d.name) for d in dests]
         f = torch.from_numpy(np.tile(feats, (T + 1, 1))).cuda()
         r = torch.from_numpy(np.repeat(np.asarray(rows, np.uint8), n)).cuda()
         p = pred.predict_batch(f, r)                      # [(T + 1) n]: origin first
-        rt = torch.from_numpy(np.array([op.run_time_ms for op in ops], np.float32)).cuda()
+        rt = torch.from_numpy(rt_host).cuda()
         neg = torch.zeros(1, dtype=torch.int32, device="cuda").view(torch.uint32)
         ms = batched.special_scale(rt.repeat(T), p[n:], p[:n].repeat(T), neg).view(T, n).cpu().numpy()
         pred._handle.check_status()
         if int(neg.view(torch.int32).cpu()[0]):
             ph = p.cpu().numpy().astype(np.float64)
             for t in range(T):
-                raw = np.array([op.run_time_ms for op in ops]) * ph[(t + 1) * n:(t + 2) * n] / ph[:n]
+                raw = rt_host.astype(np.float64) * ph[(t + 1) * n:(t + 2) * n] / ph[:n]
                 for j in np.nonzero(raw < 0)[0]:
                     logger.warning("Operation %s predicted run time %.2f ms", name, raw[j])
         return ms

@@ -25,7 +25,8 @@ class Trace:
     @property
     def run_time_ms(self):
         if self._run_time_ms is None:
-            self._run_time_ms = sum(op.run_time_ms for op in self._operations)
+            total = getattr(self._operations, "total_run_time_ms", None)   # predicted: summed already
+            self._run_time_ms = total if total is not None else sum(op.run_time_ms for op in self._operations)
         return self._run_time_ms
 
     @classmethod

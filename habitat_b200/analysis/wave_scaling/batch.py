@@ -111,11 +111,12 @@ def scale_kernels(kernels, origin_device, dest_devices, metadata_manager, mode=U
                     m[d, i] = r
         if (m >= 0).any():
             dest_regs = torch.from_numpy(m).cuda()
-    return batched.wave_scale(kb, origin_device, dest_devices, dest_regs=dest_regs, metrics=mb,
-                              want_status=True)
+    return batched.wave_scale(kb, origin_device, dest_devices, dest_regs=dest_regs, metrics=mb)
 
 
-def raise_like_reference(status_host):
-    """The reference divides by a zero wave size for these pairs."""
-    if (status_host >= 2).any():
+def raise_like_reference(scaled_ns_host):
+    """The reference divides by a zero wave size for the pairs whose predicted time the
+    kernel leaves as NaN (roofline.py:29-45: a kernel the origin cannot run at all, or one
+    that fits in an origin wave going to a device that cannot run it)."""
+    if np.isnan(scaled_ns_host).any():
         raise ZeroDivisionError("integer division or modulo by zero")

@@ -13,8 +13,9 @@ from habitat_b200.analysis.wave_scaling import batch
 def roofline_wave_scaling(kernel, origin_device, dest_device, metadata_manager):
     res = batch.scale_kernels([kernel], origin_device, [dest_device], metadata_manager,
                               mode=batch.ROOFLINE)
-    batch.raise_like_reference(res.status.cpu().numpy())
-    return PredictedKernel(kernel, float(res.scaled_ns.cpu()[0, 0]))
+    scaled = res.scaled_ns.cpu().numpy()
+    batch.raise_like_reference(scaled)
+    return PredictedKernel(kernel, float(scaled[0, 0]))
 
 
 roofline_wave_scaling.batch_mode = batch.ROOFLINE

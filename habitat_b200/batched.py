@@ -147,8 +147,7 @@ def wave_scale(kernels: KernelBatch, origin, dests: Sequence, dest_regs=None, me
     return out
 
 
-WAVE_PATHS = {0: "none", 1: "wave_scale_kernel", 2: "wave_scale_fast_kernel", 3: "wave_scale_class_kernel",
-              4: "wave_scale_lut_kernel"}
+WAVE_PATHS = {0: "none", 1: "wave_scale_kernel", 2: "wave_scale_fast_kernel", 4: "wave_scale_lut_kernel"}
 
 
 def wave_scale_path():
@@ -241,9 +240,14 @@ class MLPHandle:
         return out
 
     def check_status(self):
-        """Synchronises and raises if a launch gave up on a bounded device wait."""
+        """Synchronises and raises if a launch gave up on a bounded device wait (reported once:
+        the next call judges the launches after this one)."""
         code = ctypes.c_int32(0)
         _native.check(_native.load().hb_mlp_status(self._handle, ctypes.byref(code)))
+
+    def inject_status(self, code):
+        """Writes the device status word from the host (tests of the error path)."""
+        _native.check(_native.load().hb_mlp_inject_status(self._handle, int(code)))
 
     def phase_cycles(self):
         """Cycle counters of the first cluster in the last bf16 launch (synchronises): epilogue group 0
@@ -309,4 +313,23 @@ def plane_sum(values, out=None):
         if out.numel() != P:
             raise ValueError("out must have one entry per plane")
     _native.check(lib.hb_plane_sum(_ptr(values), L, P, _ptr(out), _native.current_stream_ptr()))
+    return out
+
+
+def group_sum(values, keys, n_groups, out=None):
+    """float64 sums of a float32 CUDA vector grouped by a uint8 key per element (keys at or above
+    n_groups and NaN values are skipped): per-device totals of a batch of MLP predictions."""
+    lib = _native.load()
+    _require_cuda(values, torch.float32, "values")
+    _require_cuda(keys, torch.uint8, "keys")
+    if values.numel() != keys.numel():
+        raise ValueError("values and keys must have the same length")
+    if out is None:
+        out = torch.empty((n_groups,), dtype=torch.float64, device=values.device)
+    else:
+        _require_cuda(out, torch.float64, "out")
+        if out.numel() != n_groups:
+            raise ValueError("out must have one entry per group")
+    _native.check(lib.hb_group_sum(_ptr(values), _ptr(keys), values.numel(), n_groups, _ptr(out),
+                                   _native.current_stream_ptr()))
     return out

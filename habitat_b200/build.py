@@ -39,33 +39,47 @@ def _stale(target, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False, ptxas_info=False):
-    """Compile every CUDA source and link the shared library. Returns its path."""
+# Sources that carry index checks under -DHB_BOUNDS_CHECK (the checked library reuses the
+# ordinary objects of the others).
+CHECKED_SOURCES = ["wave_scale.cu"]
+CHECKED_LIB_PATH = os.path.join(LIB_DIR, "libhabitat_b200_checked.so")
+
+
+def build(force=False, verbose=False, ptxas_info=False, checked=False):
+    """Compile every CUDA source and link the shared library. Returns its path.
+    checked=True builds the variant whose wave-scaling kernels compare every table and element
+    index with its bound (libhabitat_b200_checked.so; load it with HABITAT_B200_LIB=...)."""
     os.makedirs(OBJ_DIR, exist_ok=True)
     headers = [os.path.join(SRC_DIR, f) for f in os.listdir(SRC_DIR)
                if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(INCLUDE_DIR, "habitat_b200.h"))
     objs = []
     relink = force
+    lib_path = CHECKED_LIB_PATH if checked else LIB_PATH
     for src in SOURCES:
         src_path = os.path.join(SRC_DIR, src)
-        obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
+        with_checks = checked and src in CHECKED_SOURCES
+        obj = os.path.join(OBJ_DIR, src.replace(".cu", ".checked.o" if with_checks else ".o"))
         objs.append(obj)
         if force or _stale(obj, [src_path] + headers):
             cmd = [_nvcc()] + NVCC_FLAGS + ["-I", INCLUDE_DIR, "-I", SRC_DIR, "-c", src_path, "-o", obj]
+            if with_checks:
+                cmd += ["-DHB_BOUNDS_CHECK"]
             if ptxas_info:
                 cmd += ["-Xptxas", "-v"]
             if verbose:
                 print(" ".join(cmd), file=sys.stderr)
             subprocess.run(cmd, check=True)
             relink = True
-    if relink or not os.path.exists(LIB_PATH):
-        cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB_PATH] + objs + ["-cudart", "static"]
+    if relink or not os.path.exists(lib_path) or _stale(lib_path, objs):
+        cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", lib_path] + objs + ["-cudart", "static"]
         if verbose:
             print(" ".join(cmd), file=sys.stderr)
         subprocess.run(cmd, check=True)
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv))
+    if "--checked" in sys.argv:
+        print(build(verbose=True, checked=True))

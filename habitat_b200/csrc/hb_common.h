@@ -4,7 +4,10 @@
 #include <cuda_runtime.h>
 
 #include <cstdarg>
+#include <cstddef>
+#include <cstdint>
 #include <cstdio>
+#include <mutex>
 
 #include "habitat_b200.h"
 
@@ -18,6 +21,43 @@ inline hb_status cuda_fail(cudaError_t e, const char* what) {
   return HB_ERR_CUDA;
 }
 
+}  // namespace hb
+
+// ---------------------------------------------------------------------------
+// Staging for the `_host` entry points: one device block per GPU that only ever
+// grows, and one non-blocking stream per GPU, both kept for the life of the
+// process.  A `_host` call holds the arena's mutex from its first copy to its
+// final synchronise, so calls on one GPU run one after the other and the block
+// can be re-carved (and, when too small, replaced) without anything in flight.
+// ---------------------------------------------------------------------------
+namespace hb {
+struct HostArena {
+  std::mutex mu;
+  void* base = nullptr;
+  size_t bytes = 0;
+  cudaStream_t stream = nullptr;
+};
+// The arena of the current CUDA device (created, with its stream, on first use).
+hb_status arena_for_current_device(HostArena** out);
+// Makes the block at least `bytes` large.  Call with the arena's mutex held.
+hb_status arena_reserve(HostArena* arena, size_t bytes);
+
+// Hands out 256-byte aligned pieces of a block; with a null base it only adds up sizes.
+class Carver {
+ public:
+  explicit Carver(void* base) : base_(static_cast<uint8_t*>(base)) {}
+  template <typename T>
+  T* take(size_t count) {
+    const size_t at = off_;
+    off_ += (count * sizeof(T) + 255) & ~static_cast<size_t>(255);
+    return base_ ? reinterpret_cast<T*>(base_ + at) : nullptr;
+  }
+  size_t used() const { return off_; }
+
+ private:
+  uint8_t* base_;
+  size_t off_ = 0;
+};
 }  // namespace hb
 
 #define HB_CUDA_TRY(expr)                                   \

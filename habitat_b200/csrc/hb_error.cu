@@ -21,6 +21,48 @@ bool overlapped_launch_enabled() {
   }();
   return on;
 }
+
+namespace {
+constexpr int kArenaDevices = 64;
+HostArena g_arena[kArenaDevices];
+std::mutex g_arena_mu;
+}  // namespace
+
+hb_status arena_for_current_device(HostArena** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kArenaDevices) {
+    set_error("device ordinal %d out of range", dev);
+    return HB_ERR_UNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(g_arena_mu);
+  HostArena& a = g_arena[dev];
+  if (!a.stream) {
+    e = cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreateWithFlags");
+  }
+  *out = &a;
+  return HB_OK;
+}
+
+hb_status arena_reserve(HostArena* a, size_t bytes) {
+  if (bytes <= a->bytes) return HB_OK;
+  // nothing of an earlier call is in flight: every `_host` call ends with a synchronise
+  if (a->base) cudaFree(a->base);
+  a->base = nullptr;
+  a->bytes = 0;
+  const size_t want = bytes + bytes / 4;   // head room, so that slowly growing batches do not reallocate each time
+  cudaError_t e = cudaMalloc(&a->base, want);
+  if (e != cudaSuccess) {
+    e = cudaMalloc(&a->base, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc (host-entry staging)");
+    a->bytes = bytes;
+    return HB_OK;
+  }
+  a->bytes = want;
+  return HB_OK;
+}
 }  // namespace hb
 
 extern "C" const char* hb_last_error(void) { return t_error; }

@@ -44,6 +44,7 @@
 
 #include <cmath>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "hb_common.h"
@@ -1308,6 +1309,13 @@ extern "C" hb_status hb_mlp_predict(hb_mlp* h, const float* op_features, const u
     return HB_ERR_INVALID_ARGUMENT;
   }
   if (Q == 0) return HB_OK;
+  int cur = -1;
+  HB_CUDA_TRY(cudaGetDevice(&cur));
+  if (cur != h->device) {
+    // the weight pack, the tensor maps and the status word live on the GPU the handle was created on
+    hb::set_error("hb_mlp_predict: the handle belongs to CUDA device %d but device %d is current", h->device, cur);
+    return HB_ERR_INVALID_ARGUMENT;
+  }
   const bool split = h->precision == HB_PRECISION_BF16X3;
   const int tile_q = split ? 32 : kPairQ;
   const int64_t tiles = (Q + tile_q - 1) / tile_q;
@@ -1343,11 +1351,23 @@ extern "C" hb_status hb_mlp_status(hb_mlp* h, int32_t* device_status) {
     hb::set_error("hb_mlp_status: NULL argument");
     return HB_ERR_INVALID_ARGUMENT;
   }
+  HB_CUDA_TRY(cudaDeviceSynchronize());   // launches on non-blocking streams included
   HB_CUDA_TRY(cudaMemcpy(device_status, h->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
   if (*device_status != 0) {
+    // reported once: the word is cleared so that later launches are judged on their own
+    HB_CUDA_TRY(cudaMemset(h->status, 0, sizeof(int32_t)));
     hb::set_error("mlp kernel: a bounded device-side wait ran out (site 0x%x)", *device_status);
     return HB_ERR_DEVICE_TIMEOUT;
   }
+  return HB_OK;
+}
+
+extern "C" hb_status hb_mlp_inject_status(hb_mlp* h, int32_t device_status) {
+  if (!h) {
+    hb::set_error("hb_mlp_inject_status: NULL handle");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  HB_CUDA_TRY(cudaMemcpy(h->status, &device_status, sizeof(int32_t), cudaMemcpyHostToDevice));
   return HB_OK;
 }
 
@@ -1369,25 +1389,27 @@ extern "C" hb_status hb_mlp_predict_host(hb_mlp* h, const float* op_features,
     return HB_ERR_INVALID_ARGUMENT;
   }
   if (Q == 0) return HB_OK;
-  float* d_f = nullptr; uint8_t* d_r = nullptr; float* d_o = nullptr;
-  const size_t fb = sizeof(float) * static_cast<size_t>(Q) * h->n_op_feat;
-  hb_status st = HB_OK;
-  cudaError_t e;
-  if ((e = cudaMalloc(reinterpret_cast<void**>(&d_f), fb)) != cudaSuccess ||
-      (e = cudaMalloc(reinterpret_cast<void**>(&d_r), static_cast<size_t>(Q))) != cudaSuccess ||
-      (e = cudaMalloc(reinterpret_cast<void**>(&d_o), sizeof(float) * static_cast<size_t>(Q))) != cudaSuccess ||
-      (e = cudaMemcpyAsync(d_f, op_features, fb, cudaMemcpyHostToDevice, nullptr)) != cudaSuccess ||
-      (e = cudaMemcpyAsync(d_r, device_row, static_cast<size_t>(Q), cudaMemcpyHostToDevice, nullptr)) != cudaSuccess) {
-    st = hb::cuda_fail(e, "hb_mlp_predict_host: staging");
-  }
-  if (st == HB_OK) st = hb_mlp_predict(h, d_f, d_r, Q, d_o, nullptr);
-  if (st == HB_OK &&
-      (e = cudaMemcpy(out, d_o, sizeof(float) * static_cast<size_t>(Q), cudaMemcpyDeviceToHost)) != cudaSuccess)
-    st = hb::cuda_fail(e, "hb_mlp_predict_host: copy back");
-  if (st == HB_OK) {
-    int32_t code = 0;
-    st = hb_mlp_status(h, &code);
-  }
-  cudaFree(d_f); cudaFree(d_r); cudaFree(d_o);
-  return st;
+  // staged through the per-GPU block and stream the `_host` entry points share
+  hb::HostArena* arena = nullptr;
+  hb_status st = hb::arena_for_current_device(&arena);
+  if (st != HB_OK) return st;
+  std::lock_guard<std::mutex> lock(arena->mu);
+  const size_t q = static_cast<size_t>(Q);
+  hb::Carver sizes(nullptr);
+  sizes.take<float>(q * h->n_op_feat); sizes.take<uint8_t>(q); sizes.take<float>(q);
+  st = hb::arena_reserve(arena, sizes.used());
+  if (st != HB_OK) return st;
+  hb::Carver c(arena->base);
+  float* d_f = c.take<float>(q * h->n_op_feat);
+  uint8_t* d_r = c.take<uint8_t>(q);
+  float* d_o = c.take<float>(q);
+  cudaStream_t s = arena->stream;
+  HB_CUDA_TRY(cudaMemcpyAsync(d_f, op_features, sizeof(float) * q * h->n_op_feat, cudaMemcpyHostToDevice, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(d_r, device_row, q, cudaMemcpyHostToDevice, s));
+  st = hb_mlp_predict(h, d_f, d_r, Q, d_o, s);
+  if (st != HB_OK) return st;
+  HB_CUDA_TRY(cudaMemcpyAsync(out, d_o, sizeof(float) * q, cudaMemcpyDeviceToHost, s));
+  HB_CUDA_TRY(cudaStreamSynchronize(s));
+  int32_t code = 0;
+  return hb_mlp_status(h, &code);
 }

@@ -10,6 +10,8 @@
 // Sums are accumulated in float64 with a fixed assignment of elements to lanes
 // and a fixed reduction tree, so the result does not depend on grid size or
 // scheduling (no floating-point atomics).
+#include <mutex>
+
 #include "hb_common.h"
 
 namespace {
@@ -102,11 +104,82 @@ special_scale_kernel(const float* __restrict__ run_time_ms, const float* __restr
   }
 }
 
-// Scratch for the plane sum's partials, grown on demand per process.
-double* g_partial = nullptr;
-size_t g_partial_planes = 0;
+// Stage 1 of the group sum: values carry a small group key each (the device row of an MLP
+// query); a block sums a fixed contiguous chunk into one accumulator per group.  Keys at or
+// above n_groups and NaN values are skipped.
+constexpr int kGroupBlocks = 256;
+constexpr int kMaxGroups = 8;     // groups per pass; more groups take more passes
+
+__global__ void __launch_bounds__(kSumThreads)
+group_partial_kernel(const float* __restrict__ values, const uint8_t* __restrict__ keys, int64_t n,
+                     int32_t group0, int32_t n_groups, double* __restrict__ partial) {
+  hb_grid_dependency_wait();
+  const int64_t chunk = (n + kGroupBlocks - 1) / kGroupBlocks;
+  const int64_t lo = static_cast<int64_t>(blockIdx.x) * chunk;
+  const int64_t hi = lo + chunk < n ? lo + chunk : n;
+  double acc[kMaxGroups];
+#pragma unroll
+  for (int g = 0; g < kMaxGroups; ++g) acc[g] = 0.0;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += kSumThreads) {
+    const float x = values[i];
+    const int key = static_cast<int>(keys[i]) - group0;
+    const double v = x == x ? static_cast<double>(x) : 0.0;
+#pragma unroll
+    for (int g = 0; g < kMaxGroups; ++g) acc[g] += key == g ? v : 0.0;
+  }
+#pragma unroll
+  for (int g = 0; g < kMaxGroups; ++g) {
+    const double t = block_sum(acc[g]);
+    if (threadIdx.x == 0 && g < n_groups) partial[g * kGroupBlocks + blockIdx.x] = t;
+  }
+}
+
+// Per-GPU scratch of the two-stage sums.  A buffer that a launch may still be reading (or
+// that a captured graph refers to) is never freed: when more room is needed a larger buffer
+// is allocated and the old one is kept until the process ends.
+constexpr int kMaxCudaDevices = 64;
+struct SumScratch {
+  double* plane = nullptr;      // [planes][kPlaneBlocks]
+  size_t planes = 0;
+  double* group = nullptr;      // [kMaxGroups][kGroupBlocks]
+};
+SumScratch g_scratch[kMaxCudaDevices];
+std::mutex g_scratch_mu;
+
+// Scratch of the current GPU with room for `planes` plane sums (0: leave as is) and, when
+// `want_group`, for the group sum.  Allocates on the first call that needs more.
+hb_status scratch_for_current_device(size_t planes, bool want_group, SumScratch* out) {
+  int dev = 0;
+  HB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxCudaDevices) {
+    hb::set_error("device ordinal %d out of range", dev);
+    return HB_ERR_UNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  SumScratch& sc = g_scratch[dev];
+  if (planes > sc.planes) {
+    // at least 64 planes, then doubling: a handful of allocations over the life of the process
+    size_t want = sc.planes ? sc.planes : 64;
+    while (want < planes) want *= 2;
+    double* fresh = nullptr;
+    HB_CUDA_TRY(cudaMalloc(&fresh, sizeof(double) * kPlaneBlocks * want));
+    sc.plane = fresh;   // the previous buffer stays allocated: launches in flight and graphs may hold it
+    sc.planes = want;
+  }
+  if (want_group && !sc.group) HB_CUDA_TRY(cudaMalloc(&sc.group, sizeof(double) * kMaxGroups * kGroupBlocks));
+  *out = sc;
+  return HB_OK;
+}
 
 }  // namespace
+
+// Current size, in planes, of the plane-sum scratch of CUDA device `device` (0: none yet).
+// For tests of the per-GPU bookkeeping; no reference counterpart.
+extern "C" int64_t hb_plane_sum_scratch_planes(int32_t device) {
+  if (device < 0 || device >= kMaxCudaDevices) return -1;
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  return static_cast<int64_t>(g_scratch[device].planes);
+}
 
 extern "C" hb_status hb_segment_sum(const float* values, const int64_t* offsets,
                                     int64_t n_segments, double* out, void* stream) {
@@ -129,18 +202,37 @@ extern "C" hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_
     return HB_ERR_INVALID_ARGUMENT;
   }
   if (n_planes == 0) return HB_OK;
-  if (static_cast<size_t>(n_planes) > g_partial_planes) {
-    if (g_partial) cudaFree(g_partial);
-    g_partial = nullptr;
-    g_partial_planes = 0;
-    HB_CUDA_TRY(cudaMalloc(&g_partial, sizeof(double) * kPlaneBlocks * n_planes));
-    g_partial_planes = n_planes;
-  }
+  SumScratch sc;
+  const hb_status st = scratch_for_current_device(static_cast<size_t>(n_planes), false, &sc);
+  if (st != HB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(kPlaneBlocks, n_planes), dim3(kSumThreads), 0, s,
-                                    values, plane_len, g_partial));
+                                    values, plane_len, sc.plane));
   HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel, dim3(n_planes), dim3(kSumThreads), 0, s,
-                                    static_cast<const double*>(g_partial), out));
+                                    static_cast<const double*>(sc.plane), out));
+  return HB_OK;
+}
+
+extern "C" hb_status hb_group_sum(const float* values, const uint8_t* keys, int64_t n, int32_t n_groups,
+                                  double* out, void* stream) {
+  if (n < 0 || n_groups < 0 || n_groups > 256 || (n_groups > 0 && !out) || (n > 0 && (!values || !keys))) {
+    hb::set_error("hb_group_sum: bad arguments");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  if (n_groups == 0) return HB_OK;
+  SumScratch sc;
+  const hb_status st = scratch_for_current_device(0, true, &sc);
+  if (st != HB_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // eight groups per pass; the passes share the scratch and follow one another on the stream
+  for (int32_t g0 = 0; g0 < n_groups; g0 += kMaxGroups) {
+    const int32_t ng = n_groups - g0 < kMaxGroups ? n_groups - g0 : kMaxGroups;
+    HB_CUDA_TRY(hb::launch_overlapped(group_partial_kernel, dim3(kGroupBlocks), dim3(kSumThreads), 0, s, values,
+                                      keys, n, g0, ng, sc.group));
+    static_assert(kGroupBlocks == kPlaneBlocks, "the final stage is shared with the plane sum");
+    HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel, dim3(ng), dim3(kSumThreads), 0, s,
+                                      static_cast<const double*>(sc.group), out + g0));
+  }
   return HB_OK;
 }
 
@@ -175,7 +267,6 @@ constexpr int kStaticPlanes = 64;
 static __device__ __align__(256) double g_static_partial[kStaticPlanes * kPlaneBlocks];
 
 namespace {
-constexpr int kMaxCudaDevices = 64;
 // Device address of g_static_partial on each device, resolved on first use.  In
 // host code the symbol's name is only a handle for the runtime, not an address a
 // kernel could dereference, hence the look-up.

@@ -13,9 +13,11 @@
 // per-launch (origin, destination) log2 ratios travel as a kernel parameter.
 // The kernel is HBM-bound by design: 20 B read + 5 B written per kernel and
 // 9 B written per pair.
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "hb_common.h"
@@ -26,11 +28,6 @@ namespace {
 thread_local int32_t t_path = 0;   // kernel of the last launch, see hb_wave_scale_path
 
 __constant__ hb_dev_pre c_dev[HB_MAX_DEVICES];
-
-// Host mirror of the uploaded table (ratios are formed from the raw rows).
-hb_device_spec g_rows[HB_MAX_DEVICES];
-hb_dev_pre g_pre[HB_MAX_DEVICES];
-int g_n_rows = 0;
 
 struct LaunchParams {
   int32_t D;
@@ -350,36 +347,87 @@ bool vec4_ok(const Ptrs& p, int64_t K, bool need_gamma) {
 }
 
 // ---------------------------------------------------------------------------
-// Class kernel.  Device rows usually differ in only a few of the fields the
-// occupancy rules read (all six benchmark rows share one register file shape,
-// two warp budgets and three shared-memory budgets).  The host groups the rows
-// of a launch into classes per limit; a thread evaluates each class once per
-// kernel record and a destination only picks its three limits and takes the
-// minimum.  Up to four classes per limit, no per-destination register
-// overrides; anything else takes wave_scale_fast_kernel.
+// Table kernel.  Every device-dependent limit of a record is a function of small
+// integers, so hb_set_devices tabulates, per device row and one byte each:
+//   P[warps per block 0..33][256-register units per warp 0..33] =
+//       min(register limit, warp limit, blocks-per-SM limit)
+//   S[shared memory in 128-byte steps 0..2047] = shared-memory limit
+// and, per occupancy 0..32, a 16-byte entry T[occ] = {M, sh, A_hi, A_lo}:
+//   * floor(n / (SMs * occ)) = umulhi(n, M) >> sh for every 0 <= n < 2^31
+//     (M = floor(2^(31+s) / wave) + 1 with s = ceil(log2 wave), sh = s - 1: the
+//     error term n e / 2^(31+s) stays below 1 / wave because e <= wave <= 2^s),
+//     so a pair's wave count is one table load, one multiply-high and a shift,
+//     and "the kernel fits in one wave" is the test quotient == 0;
+//   * A = log2(occ) - log2(clock MHz) as float hi + lo: the exponent of the
+//     small-kernel rule (roofline.py:32-45) is (1 - gamma) (A_dest[blocks per SM
+//     on the destination] - A_origin[blocks per SM on the origin]).
+// Rows that agree on everything P (or S) reads form a class; a launch carries at
+// most four classes of each, a record loads one byte per class, and a
+// destination picks its two bytes with a byte permute and takes one 16-bit-pair
+// minimum for the two records a thread owns.  The tables a launch touches
+// (a few KB) stay in L1.  The extended variant (EXT) reads every device's own P and S
+// bytes per pair instead (no class limit) and adds, under launch-uniform branches,
+// the status plane, per-destination register counts and gamma from raw metrics
+// (one float64 intensity per record, a compare and a multiply-add per pair); it
+// also serves launches with more than four classes.  The grid is persistent:
+// blocks stride over the batch.
+// Conditions (checked on the host, else wave_scale_fast_kernel or the generic
+// kernel runs): D <= 32, D K < 2^31, and per row 2 <= SMs <= 4096,
+// blocks-per-SM limit <= 32, thread limit per block a multiple of 32 and <= 1024,
+// shared-memory reserve a multiple of 128, shared-memory cap below the table's
+// last step.
 // ---------------------------------------------------------------------------
 constexpr int kMaxClasses = 4;
+constexpr int kLutW = 34;      // warps per block 0..32, 33 = more
+constexpr int kLutU = 34;      // register units per warp 0..32, 33 = more than 256 registers
+constexpr int kLutP = kLutW * kLutU;
+constexpr int kLutS = 2048;    // shared memory in 128-byte steps, last entry = above every cap
+constexpr int kLutOcc = 33;    // occupancies 0..32
 
-struct ClassDev {
-  int32_t num_sms;
-  uint32_t sms_magic;
-  float a_hi, a_lo, b_hi, b_lo;
-  float clk_hi, clk_lo;     // log2 of the clock ratio, split
-  uint8_t rc, wc, sc, blocks_limit;
+struct alignas(16) LutOcc {
+  uint32_t magic, shift;
+  float lg_hi, lg_lo;
 };
 
-struct ClassParams {
-  int32_t D, n_rc, n_wc, n_sc;
-  int64_t K;
-  FastDev cls_r[kMaxClasses], cls_w[kMaxClasses], cls_s[kMaxClasses];
-  ClassDev origin;
-  ClassDev dest[HB_MAX_DEVICES / 2];
-};
+__device__ uint8_t g_lut_p[HB_MAX_DEVICES * kLutP];
+__device__ uint8_t g_lut_s[HB_MAX_DEVICES * kLutS];
+__device__ LutOcc g_lut_t[HB_MAX_DEVICES * kLutOcc];
 
-// Byte c of a packed word (one permute instruction).
-__device__ __forceinline__ int32_t pick_byte(uint32_t packed, uint32_t c) {
-  return static_cast<int32_t>(__byte_perm(packed, 0u, 0x4440u | c));
+struct alignas(16) LutDev {       // three 16-byte groups, each fetched with one constant load
+  uint32_t sel_p, sel_s;          // permute selectors: class byte of record 0 -> low half, record 1 -> high half
+  uint32_t t_off;                 // byte offset of the row's T entries
+  uint32_t p_off;                 // byte offset of the row's own P table (per-destination register counts)
+  float a_hi, a_lo, b_hi, b_lo;   // large-kernel exponent gamma a + b, split float64 constants
+  uint32_t sms_m1, sms_magic;     // SMs - 1 and floor(2^32 / SMs) + 1, for ceil(blocks / SMs)
+  uint32_t s_off;                 // byte offset of the row's own S table (extended variant)
+  uint32_t pad;
+};
+struct LutDevRegs {               // LutDev as read by a thread
+  uint4 sel;
+  float4 ab;
+  uint4 sm;
+};
+__device__ __forceinline__ LutDevRegs load_lut_dev(const LutDev& d) {
+  LutDevRegs r;
+  r.sel = *reinterpret_cast<const uint4*>(&d.sel_p);
+  r.ab = *reinterpret_cast<const float4*>(&d.a_hi);
+  r.sm = *reinterpret_cast<const uint4*>(&d.sms_m1);
+  return r;
 }
+
+struct LutParams {
+  uint32_t K;
+  int32_t D;
+  uint32_t off_p[kMaxClasses], off_s[kMaxClasses];   // byte offsets of the class tables
+  double origin_peak;                                // metrics mode: origin peak GFLOP/s
+  LutDev origin;
+  LutDev dest[HB_MAX_DEVICES / 2];
+  double ridge[HB_MAX_DEVICES / 2];                  // metrics mode: destination peak / bandwidth
+  double slope[HB_MAX_DEVICES / 2];                  // -0.5 / ridge
+};
+
+constexpr int kLutThreads = 128;
+
 // prmt.b32 in its default mode: selector nibble n picks byte (n & 7) of {b, a}; with bit 3 set
 // the byte's sign bit is replicated instead (0x00 for the values below 128 used here).
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -393,349 +441,324 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-template <int VEC>
-__global__ void __launch_bounds__(128)
-wave_scale_class_kernel(const Ptrs p, const __grid_constant__ ClassParams cp) {
-  __shared__ uint32_t s_magic[kMagicN];
-  __shared__ uint32_t s_wave_magic[HB_MAX_DEVICES / 2 + 1][33];
-  __shared__ float2 s_log2[33];   // log2(i) as float hi + lo
-  for (int i = threadIdx.x; i < kMagicN; i += blockDim.x) s_magic[i] = g_magic[i];
-  for (int i = threadIdx.x; i < (cp.D + 1) * 33; i += blockDim.x) {
-    const int d = i / 33, occ = i - d * 33;
-    const uint32_t wave = static_cast<uint32_t>((d == 0 ? cp.origin.num_sms : cp.dest[d - 1].num_sms) * occ);
-    s_wave_magic[d][occ] = wave >= 2u ? 0xFFFFFFFFu / wave + ((0xFFFFFFFFu % wave) + 1u == wave ? 1u : 0u) + 1u : 0u;
+#if defined(HB_BOUNDS_CHECK)
+// Checked build: every table index and element index is compared with its bound; a violation is
+// recorded (first one wins) and the access redirected to element 0.  Nothing traps.
+__device__ uint32_t g_bounds_word = 0;
+__device__ __forceinline__ uint32_t hb_checked(uint32_t idx, uint32_t limit, uint32_t site) {
+  if (idx >= limit) {
+    atomicCAS(&g_bounds_word, 0u, (site << 24) | (idx & 0xFFFFFFu) | 0x80000000u);
+    return 0u;
   }
-  if (threadIdx.x < 33) {
-    const double l = c_log2_int[threadIdx.x];
-    const float hi = static_cast<float>(l);
-    s_log2[threadIdx.x] = make_float2(hi, static_cast<float>(l - static_cast<double>(hi)));
-  }
-  __syncthreads();
-
-  const int64_t K = cp.K;
-  const int64_t k0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
-  if (k0 >= K) return;
-
-  const Vec<int32_t, VEC> nbv = load_vec<int32_t, VEC>(p.num_blocks + k0);
-  const Vec<uint16_t, VEC> bsv = load_vec<uint16_t, VEC>(p.block_size + k0);
-  const Vec<uint16_t, VEC> rgv = load_vec<uint16_t, VEC>(p.regs + k0);
-  const Vec<uint32_t, VEC> smv = load_vec<uint32_t, VEC>(p.smem + k0);
-  const Vec<float, VEC> tv = load_vec<float, VEC>(p.time_ns + k0);
-  const Vec<float, VEC> gv = load_vec<float, VEC>(p.gamma + k0);
-
-  // the class limits of a record, one byte each (values above 255 cannot win the
-  // minimum against the blocks-per-SM limit, which is at most 32)
-  uint32_t lr[VEC], lw[VEC], ls[VEC];
-  int32_t wave_o[VEC];
-  float2 lg_o[VEC];   // log2 of the origin's per-SM block count (small-kernel branch)
-  Vec<uint8_t, VEC> oocc;
-  Vec<uint32_t, VEC> owav;
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    FastKernel k;
-    k.block_size = bsv.v[i];
-    k.wpb = (k.block_size + 31) >> 5;
-    k.regs = rgv.v[i];
-    k.rpw_units = (k.regs + 7) >> 3;
-    k.smem = smv.v[i] > 0x7FFF0000u ? -1 : static_cast<int32_t>(smv.v[i]);
-    k.m_wpb = s_magic[min(k.wpb, kMagicN - 1)];
-    const uint32_t m_rpw = s_magic[min(k.rpw_units, kMagicN - 1)];
-    lr[i] = lw[i] = ls[i] = 0;
-#pragma unroll
-    for (int c = 0; c < kMaxClasses; ++c) {
-      if (c < cp.n_rc) lr[i] |= static_cast<uint32_t>(min(fast_regs_limit(cp.cls_r[c], k, k.regs, k.rpw_units, m_rpw), 255)) << (8 * c);
-      if (c < cp.n_wc) lw[i] |= static_cast<uint32_t>(min(fast_warps_limit(cp.cls_w[c], k), 255)) << (8 * c);
-      if (c < cp.n_sc) ls[i] |= static_cast<uint32_t>(min(fast_smem_limit(cp.cls_s[c], k, s_magic), 255)) << (8 * c);
-    }
-    const int32_t occ = min(min(pick_byte(lr[i], cp.origin.rc), pick_byte(ls[i], cp.origin.sc)),
-                            min(pick_byte(lw[i], cp.origin.wc), static_cast<int32_t>(cp.origin.blocks_limit)));
-    const int32_t nb = nbv.v[i];
-    wave_o[i] = cp.origin.num_sms * occ;
-    oocc.v[i] = static_cast<uint8_t>(occ);
-    owav.v[i] = (occ > 0 && nb >= 1)
-                    ? udiv_magic_fix(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_o[i]),
-                                     s_wave_magic[0][occ])
-                    : 0xFFFFFFFFu;
-    // ceil(nb / num_sms) <= occupancy <= 32 whenever the small-kernel branch is taken
-    const uint32_t om = (nb >= 1 && nb < wave_o[i])
-                            ? udiv_magic(nb + cp.origin.num_sms - 1, cp.origin.num_sms, cp.origin.sms_magic)
-                            : 1u;
-    lg_o[i] = s_log2[om];
-  }
-  store_vec<uint8_t, VEC>(p.origin_occ + k0, oocc);
-  store_vec<uint32_t, VEC>(p.origin_waves + k0, owav);
-
-  for (int d = 0; d < cp.D; ++d) {
-    const ClassDev& dd = cp.dest[d];
-    const int64_t base = static_cast<int64_t>(d) * K + k0;
-    const uint32_t rc = dd.rc, wc = dd.wc, sc = dd.sc;
-    const int32_t bl = dd.blocks_limit;
-    Vec<float, VEC> outv;
-    Vec<uint8_t, VEC> occv;
-    Vec<uint32_t, VEC> wavv;
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      const int32_t nb = nbv.v[i];
-      const int32_t occ = min(min(pick_byte(lr[i], rc), pick_byte(ls[i], sc)), min(pick_byte(lw[i], wc), bl));
-      const int32_t wave_d = dd.num_sms * occ;
-      occv.v[i] = static_cast<uint8_t>(occ);
-      wavv.v[i] = (occ > 0 && nb >= 1)
-                      ? udiv_magic_fix(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_d),
-                                       s_wave_magic[d + 1][occ])
-                      : 0xFFFFFFFFu;
-      const float gamma = gv.v[i];
-      const bool live = nb >= 1 && wave_o[i] != 0;
-      const bool small = live && nb < wave_o[i] && nb < wave_d;
-      const bool ok = live && !(nb < wave_o[i] && wave_d == 0);
-      // small kernel (roofline.py:32-45): exponent (1 - gamma) (log2 clk + log2 dmax - log2 omax),
-      // both per-SM block counts <= 32; log2 values carried as float hi + lo
-      const uint32_t dm = small ? udiv_magic(nb + dd.num_sms - 1, dd.num_sms, dd.sms_magic) : 1u;
-      const float2 lg_d = s_log2[dm];
-      const float e_small = (1.0f - gamma) * ((lg_d.x - lg_o[i].x) + ((lg_d.y - lg_o[i].y) + dd.clk_lo) + dd.clk_hi);
-      const float e_large = fmaf(gamma, dd.a_hi, dd.b_hi) + fmaf(gamma, dd.a_lo, dd.b_lo);
-      const float e = small ? e_small : e_large;
-      outv.v[i] = ok ? tv.v[i] * ex2_approx(e) : __int_as_float(0x7FC00000);
-    }
-    store_vec<float, VEC>(p.scaled_ns + base, outv);
-    store_vec<uint8_t, VEC>(p.dest_occ + base, occv);
-    store_vec<uint32_t, VEC>(p.dest_waves + base, wavv);
-  }
+  return idx;
 }
+#define HB_IDX(idx, limit, site) hb_checked((idx), (limit), (site))
+#else
+#define HB_IDX(idx, limit, site) (idx)
+#endif
 
-// ---------------------------------------------------------------------------
-// Table kernel.  The three class limits of a record are functions of small
-// integers: the register limit of (warps per block, 256-register units per
-// warp), the warp limit of the warps per block, the shared-memory limit of the
-// request in 128-byte steps.  hb_set_devices tabulates them per device row (one
-// byte each: anything above 127 cannot win against the blocks-per-SM limit) in
-// global memory; a launch reads the rows that represent its classes through
-// L1 (a few KB), so a record costs one byte load per class instead of the limit
-// arithmetic, and the kernel needs no shared memory and no block prologue.  The
-// reciprocals of the wave sizes (SMs x occupancy) and the log2 pairs of the
-// small-kernel branch are tabulated the same way.  A thread owns two consecutive
-// records and forms both occupancies of a destination with 16-bit-pair minimum
-// instructions.
-// Conditions (checked on the host, else the class kernel runs): the class
-// kernel's own, plus K even, D K < 2^31, and per row 16 <= SMs, SMs x
-// blocks-per-SM limit inside the reciprocal table, thread limit per block a
-// multiple of 32 and <= 1024, shared-memory reserve a multiple of 128,
-// shared-memory cap below the table's last step, blocks-per-SM limit <= 127.
-// ---------------------------------------------------------------------------
-constexpr int kLutW = 34;      // warps per block 0..32, 33 = more
-constexpr int kLutU = 34;      // register units per warp 0..32, 33 = more than 256 registers
-constexpr int kLutS = 2048;    // shared memory in 128-byte steps, last entry = above every cap
-constexpr int kLutWPad = 36;
-
-__device__ uint8_t g_lut_r[HB_MAX_DEVICES][kLutW * kLutU];
-__device__ uint8_t g_lut_w[HB_MAX_DEVICES][kLutWPad];
-__device__ uint8_t g_lut_s[HB_MAX_DEVICES][kLutS];
-bool g_lut_ok[HB_MAX_DEVICES];   // host: row tabulated
-
-struct alignas(16) LutDev {       // three 16-byte groups, each fetched with one constant load
-  uint32_t sel_r, sel_w, sel_s;   // permute selectors: class byte of record 0 -> low half, record 1 -> high half
-  uint32_t bl2;                   // blocks-per-SM limit in both halves
-  float a_hi, a_lo, b_hi, b_lo;
-  int32_t num_sms;
-  uint32_t sms_magic;
-  float clk_hi, clk_lo;
-};
-struct LutDevRegs {               // LutDev as read by a thread
-  uint4 sel;                      // sel_r, sel_w, sel_s, bl2
-  float4 ab;                      // a_hi, a_lo, b_hi, b_lo
-  uint4 sm;                       // num_sms, sms_magic, clk_hi, clk_lo (bits)
-};
-__device__ __forceinline__ LutDevRegs load_lut_dev(const LutDev& d) {
-  LutDevRegs r;
-  r.sel = *reinterpret_cast<const uint4*>(&d.sel_r);
-  r.ab = *reinterpret_cast<const float4*>(&d.a_hi);
-  r.sm = *reinterpret_cast<const uint4*>(&d.num_sms);
-  return r;
-}
-
-struct LutParams {
-  int32_t D, n_rc, n_wc, n_sc;
-  int64_t K;
-  int32_t row_r[kMaxClasses], row_w[kMaxClasses], row_s[kMaxClasses];   // table rows of the classes
-  LutDev origin;
-  LutDev dest[HB_MAX_DEVICES / 2];
-};
-
-constexpr int kLutThreads = 128;
-
-__device__ float2 g_log2_pair[33];     // log2(i) as float hi + lo; filled by hb_set_devices
-constexpr int kWaveMagicN = 8192;      // wave sizes (SMs x occupancy) below this have a tabulated reciprocal
-__device__ uint32_t g_wave_magic[kWaveMagicN];
-
-// floor(n / d) for d >= 2 with M = floor(2^32 / d) + 1 and any n < 2^32.
-__device__ __forceinline__ uint32_t udiv_fix_ge2(uint32_t n, uint32_t d, uint32_t M) {
-  uint32_t q = __umulhi(n, M);
-  if (q * d > n) --q;
-  return q;
-}
-
-// 12 blocks of 128 threads per SM (40 registers) measured fastest (8, 10 and 16 were slower), and
-// so did the run-time destination loop against instances unrolled for a known destination count.
-__global__ void __launch_bounds__(kLutThreads, 12)
+template <int VEC, bool EXT, int NP, int NS>
+__global__ void __launch_bounds__(kLutThreads, EXT ? 8 : 12)
 wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
   hb_grid_dependency_wait();
+  const uint32_t K = lp.K;
   const int D = lp.D;
-  const int64_t K = lp.K;
-  const int64_t k0 = (static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x) * 2;
-  if (k0 >= K) return;
+  const uint8_t* __restrict__ tab_t = reinterpret_cast<const uint8_t*>(g_lut_t);
+  const uint32_t stride = gridDim.x * (kLutThreads * VEC);
+  const bool with_regs = EXT && p.dest_regs != nullptr;
+  const bool with_metrics = EXT && p.has_metrics != nullptr;
+  const bool with_status = EXT && p.status != nullptr;
 
-  const Vec<int32_t, 2> nbv = load_vec<int32_t, 2>(p.num_blocks + k0);
-  const Vec<uint16_t, 2> bsv = load_vec<uint16_t, 2>(p.block_size + k0);
-  const Vec<uint16_t, 2> rgv = load_vec<uint16_t, 2>(p.regs + k0);
-  const Vec<uint32_t, 2> smv = load_vec<uint32_t, 2>(p.smem + k0);
-  const Vec<float, 2> tv = load_vec<float, 2>(p.time_ns + k0);
-  const Vec<float, 2> gv = load_vec<float, 2>(p.gamma + k0);
+  for (uint32_t k0 = (blockIdx.x * kLutThreads + threadIdx.x) * VEC; k0 < K; k0 += stride) {
+    const Vec<int32_t, VEC> nbv = load_vec<int32_t, VEC>(p.num_blocks + k0);
+    const Vec<uint16_t, VEC> bsv = load_vec<uint16_t, VEC>(p.block_size + k0);
+    const Vec<uint16_t, VEC> rgv = load_vec<uint16_t, VEC>(p.regs + k0);
+    const Vec<uint32_t, VEC> smv = load_vec<uint32_t, VEC>(p.smem + k0);
+    const Vec<float, VEC> tv = load_vec<float, VEC>(p.time_ns + k0);
+    Vec<float, VEC> gv;
+    if (!with_metrics) gv = load_vec<float, VEC>(p.gamma + k0);
 
-  uint32_t lr[2], lw[2], ls[2];
-  int32_t wave_o[2];
-  float2 lg_o[2];
-  float omg[2];
-  bool live[2], lt_o[2];
+    uint32_t P[2] = {0u, 0u}, S[2] = {0u, 0u};   // class bytes of the two records
+    uint32_t wrow[2] = {0u, 0u};                 // EXT: warps per block x row length (P index base)
+    float omg[2] = {0.0f, 0.0f};
+    double xint[2] = {-1.0, -1.0}, xinv[2] = {0.0, 0.0};   // EXT: intensity (< 0: special case) and 1 / intensity
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const uint32_t wpb = min((static_cast<uint32_t>(bsv.v[i]) + 31u) >> 5, static_cast<uint32_t>(kLutW - 1));
-    const uint32_t units = min((static_cast<uint32_t>(rgv.v[i]) + 7u) >> 3, static_cast<uint32_t>(kLutU - 1));
-    const uint32_t steps = min((min(smv.v[i], static_cast<uint32_t>(kLutS) << 7) + 127u) >> 7,
-                               static_cast<uint32_t>(kLutS - 1));
-    uint32_t r = 0, w = 0, sm = 0;
+    for (int i = 0; i < VEC; ++i) {
+      const uint32_t wpb = min((static_cast<uint32_t>(bsv.v[i]) + 31u) >> 5, static_cast<uint32_t>(kLutW - 1));
+      const uint32_t units = min((static_cast<uint32_t>(rgv.v[i]) + 7u) >> 3, static_cast<uint32_t>(kLutU - 1));
+      const uint32_t pidx = HB_IDX(wpb * kLutU + units, kLutP, 1);
+      const uint32_t steps = HB_IDX((min(smv.v[i], static_cast<uint32_t>(kLutS - 1) << 7) + 127u) >> 7, kLutS, 2);
+      if (!EXT) {
+        uint32_t pw = 0, sw = 0;
 #pragma unroll
-    for (int c = 0; c < kMaxClasses; ++c) {
-      if (c < lp.n_rc) r |= static_cast<uint32_t>(__ldg(&g_lut_r[lp.row_r[c]][wpb * kLutU + units])) << (8 * c);
-      if (c < lp.n_wc) w |= static_cast<uint32_t>(__ldg(&g_lut_w[lp.row_w[c]][wpb])) << (8 * c);
-      if (c < lp.n_sc) sm |= static_cast<uint32_t>(__ldg(&g_lut_s[lp.row_s[c]][steps])) << (8 * c);
+        for (int c = 0; c < NP; ++c) pw |= static_cast<uint32_t>(__ldg(g_lut_p + (lp.off_p[c] + pidx))) << (8 * c);
+#pragma unroll
+        for (int c = 0; c < NS; ++c) sw |= static_cast<uint32_t>(__ldg(g_lut_s + (lp.off_s[c] + steps))) << (8 * c);
+        P[i] = pw; S[i] = sw;
+      } else {
+        // extended variant: every device's own tables are indexed directly (no class limit)
+        P[i] = pidx; S[i] = steps;
+        wrow[i] = wpb * kLutU;
+      }
+      if (!with_metrics) omg[i] = 1.0f - gv.v[i];
+      if (with_metrics) {
+        // wave_scaling/roofline.py:68-92, float64, same operation order
+        double x = -1.0;   // "no metrics" or next to no floating-point work: gamma = 1
+        if (p.has_metrics[k0 + i]) {
+          const double total_gb = (p.dram_read[k0 + i] + p.dram_write[k0 + i]) / 1024 / 1024 / 1024;
+          const double gps = p.flop_eff[k0 + i] / 100 * lp.origin_peak;
+          const double gf = gps * static_cast<double>(tv.v[i]) / 1e9;
+          if (gf < 1e-9) x = -1.0;
+          else if (total_gb == 0) x = -2.0;   // gamma = 0
+          else x = gf / total_gb;
+        }
+        xint[i] = x;
+        xinv[i] = x > 0.0 ? 1.0 / x : 0.0;
+      }
     }
-    lr[i] = r; lw[i] = w; ls[i] = sm;
-    omg[i] = 1.0f - gv.v[i];
-  }
-  // origin: both records at once
-  const LutDevRegs og = load_lut_dev(lp.origin);
-  const int32_t o_sms = static_cast<int32_t>(og.sm.x);
-  const uint32_t o2 = __vimin3_s16x2(
-      __vimin3_s16x2(prmt(lr[0], lr[1], og.sel.x), prmt(ls[0], ls[1], og.sel.z), prmt(lw[0], lw[1], og.sel.y)),
-      og.sel.w, og.sel.w);
-  Vec<uint32_t, 2> owav;
+
+    // origin: both records at once
+    const LutDevRegs og = load_lut_dev(lp.origin);
+    uint32_t o2;
+    if (!EXT) {
+      o2 = __vimin_s16x2_relu(prmt(P[0], P[1], og.sel.x), prmt(S[0], S[1], og.sel.y));
+    } else {
+      o2 = 0;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const uint32_t occ = i == 0 ? (o2 & 0xFFFFu) : (o2 >> 16);
-    const int32_t nb = nbv.v[i];
-    wave_o[i] = o_sms * static_cast<int32_t>(occ);
-    owav.v[i] = (occ > 0 && nb >= 1)
-                    ? udiv_fix_ge2(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_o[i]),
-                                   __ldg(&g_wave_magic[wave_o[i]]))
-                    : 0xFFFFFFFFu;
-    live[i] = nb >= 1 && occ != 0;
-    lt_o[i] = nb < wave_o[i];
-    // ceil(nb / num_sms) <= occupancy <= 32 whenever the small-kernel branch is taken
-    const uint32_t om = (nb >= 1 && lt_o[i]) ? __umulhi(nb + o_sms - 1, og.sm.y) : 1u;
-    lg_o[i] = __ldg(&g_log2_pair[om]);
-  }
-  *reinterpret_cast<uint16_t*>(p.origin_occ + k0) = static_cast<uint16_t>(__byte_perm(o2, 0u, 0x4420u));
-  store_vec<uint32_t, 2>(p.origin_waves + k0, owav);
+      for (int i = 0; i < VEC; ++i) {
+        const uint32_t pb = __ldg(g_lut_p + (og.sel.w + P[i]));
+        const uint32_t sb = __ldg(g_lut_s + (og.sm.z + S[i]));
+        o2 |= min(pb, sb) << (16 * i);
+      }
+    }
+    bool nbok[2] = {false, false}, live[2] = {false, false}, fits_o[2] = {false, false};
+    float2 lg_o[2];
+    Vec<uint32_t, VEC> owav;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const uint32_t occ = i == 0 ? (o2 & 0xFFFFu) : (o2 >> 16);
+      const int32_t nb = nbv.v[i];
+      const uint2 w = __ldg(reinterpret_cast<const uint2*>(tab_t + (og.sel.z + HB_IDX(occ, kLutOcc, 3) * 16u)));
+      const uint32_t q = __umulhi(static_cast<uint32_t>(nb), w.x) >> w.y;
+      nbok[i] = nb >= 1;
+      live[i] = nbok[i] && occ != 0u;
+      owav.v[i] = live[i] ? q : 0xFFFFFFFFu;
+      fits_o[i] = live[i] && q == 0u;            // num_blocks < origin wave size
+      // ceil(num_blocks / SMs) <= occupancy <= 32 whenever the small-kernel rule applies
+      const uint32_t om = fits_o[i] ? __umulhi(static_cast<uint32_t>(nb) + og.sm.x, og.sm.y) : 1u;
+      lg_o[i] = __ldg(reinterpret_cast<const float2*>(tab_t + (og.sel.z + HB_IDX(om, kLutOcc, 4) * 16u + 8u)));
+    }
+    if (VEC == 2) {
+      *reinterpret_cast<uint16_t*>(p.origin_occ + k0) = static_cast<uint16_t>(__byte_perm(o2, 0u, 0x4420u));
+    } else {
+      p.origin_occ[k0] = static_cast<uint8_t>(o2);
+    }
+    store_vec<uint32_t, VEC>(p.origin_waves + k0, owav);
 
 #pragma unroll 1
-  for (int d = 0; d < D; ++d) {
-    const LutDevRegs dd = load_lut_dev(lp.dest[d]);
-    const int32_t d_sms = static_cast<int32_t>(dd.sm.x);
-    const float clk_hi = __uint_as_float(dd.sm.z), clk_lo = __uint_as_float(dd.sm.w);
-    const uint32_t base = static_cast<uint32_t>(d) * static_cast<uint32_t>(K) + static_cast<uint32_t>(k0);   // D K < 2^31
-    const uint32_t occ2 = __vimin3_s16x2(
-        __vimin3_s16x2(prmt(lr[0], lr[1], dd.sel.x), prmt(ls[0], ls[1], dd.sel.z), prmt(lw[0], lw[1], dd.sel.y)),
-        dd.sel.w, dd.sel.w);
-    Vec<float, 2> outv;
-    Vec<uint32_t, 2> wavv;
+    for (int d = 0; d < D; ++d) {
+      const LutDevRegs dd = load_lut_dev(lp.dest[d]);
+      const uint32_t base = static_cast<uint32_t>(d) * K + k0;   // D K < 2^31
+      uint32_t occ2;
+      if (!EXT) {
+        occ2 = __vimin_s16x2_relu(prmt(P[0], P[1], dd.sel.x), prmt(S[0], S[1], dd.sel.y));
+      } else {
+        Vec<int16_t, VEC> drv;
+        if (with_regs) drv = load_vec<int16_t, VEC>(p.dest_regs + base);
+        occ2 = 0;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const uint32_t occ = i == 0 ? (occ2 & 0xFFFFu) : (occ2 >> 16);
-      const int32_t nb = nbv.v[i];
-      const int32_t wave_d = d_sms * static_cast<int32_t>(occ);
-      wavv.v[i] = (occ > 0 && nb >= 1)
-                      ? udiv_fix_ge2(static_cast<uint32_t>(nb), static_cast<uint32_t>(wave_d),
-                                     __ldg(&g_wave_magic[wave_d]))
-                      : 0xFFFFFFFFu;
-      const float gamma = gv.v[i];
-      const bool small = live[i] && lt_o[i] && nb < wave_d;
-      const bool ok = live[i] && !(lt_o[i] && occ == 0);
-      // small kernel (roofline.py:32-45): exponent (1 - gamma) (log2 clk + log2 dmax - log2 omax),
-      // both per-SM block counts <= 32; log2 values carried as float hi + lo
-      const uint32_t dm = small ? __umulhi(nb + d_sms - 1, dd.sm.y) : 1u;
-      const float2 lg_d = __ldg(&g_log2_pair[dm]);
-      const float e_small = omg[i] * ((lg_d.x - lg_o[i].x) + ((lg_d.y - lg_o[i].y) + clk_lo) + clk_hi);
-      const float e_large = fmaf(gamma, dd.ab.x, dd.ab.z) + fmaf(gamma, dd.ab.y, dd.ab.w);
-      const float e = small ? e_small : e_large;
-      outv.v[i] = ok ? tv.v[i] * ex2_approx(e) : __int_as_float(0x7FC00000);
+        for (int i = 0; i < VEC; ++i) {
+          uint32_t pidx = P[i];
+          if (with_regs && drv.v[i] >= 0) {
+            // MetadataManager.kernel_registers_for gave another register count for this destination
+            const uint32_t units = min((static_cast<uint32_t>(drv.v[i]) + 7u) >> 3, static_cast<uint32_t>(kLutU - 1));
+            pidx = HB_IDX(wrow[i] + units, kLutP, 5);
+          }
+          const uint32_t pb = __ldg(g_lut_p + (dd.sel.w + pidx));
+          const uint32_t sb = __ldg(g_lut_s + (dd.sm.z + S[i]));
+          occ2 |= min(pb, sb) << (16 * i);
+        }
+      }
+      Vec<float, VEC> outv;
+      Vec<uint32_t, VEC> wavv;
+      uint32_t st2 = 0;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const uint32_t occ = i == 0 ? (occ2 & 0xFFFFu) : (occ2 >> 16);
+        const int32_t nb = nbv.v[i];
+        const uint2 w = __ldg(reinterpret_cast<const uint2*>(tab_t + (dd.sel.z + HB_IDX(occ, kLutOcc, 6) * 16u)));
+        const uint32_t q = __umulhi(static_cast<uint32_t>(nb), w.x) >> w.y;
+        const bool has_wave = occ != 0u;
+        wavv.v[i] = (nbok[i] && has_wave) ? q : 0xFFFFFFFFu;
+        // roofline.py:29-30 with its short circuit: the destination is only looked at when the
+        // kernel fits in one origin wave
+        const bool small = fits_o[i] && has_wave && q == 0u;
+        const bool ok = live[i] && !(fits_o[i] && !has_wave);
+        const uint32_t dm = small ? __umulhi(static_cast<uint32_t>(nb) + dd.sm.x, dd.sm.y) : 1u;
+        const float2 lg_d = __ldg(reinterpret_cast<const float2*>(tab_t + (dd.sel.z + HB_IDX(dm, kLutOcc, 7) * 16u + 8u)));
+        float gamma, one_minus;
+        if (with_metrics) {
+          const double x = xint[i];
+          double gm;
+          if (x < 0.0) gm = x == -1.0 ? 1.0 : 0.0;
+          else gm = x > lp.ridge[d] ? 0.5 * lp.ridge[d] * xinv[i] : fma(lp.slope[d], x, 1.0);
+          gamma = static_cast<float>(gm);
+          one_minus = static_cast<float>(1.0 - gm);
+        } else {
+          gamma = gv.v[i];
+          one_minus = omg[i];
+        }
+        const float e_small = one_minus * ((lg_d.x - lg_o[i].x) + (lg_d.y - lg_o[i].y));
+        const float e_large = fmaf(gamma, dd.ab.x, dd.ab.z) + fmaf(gamma, dd.ab.y, dd.ab.w);
+        const float e = small ? e_small : e_large;
+        outv.v[i] = ok ? tv.v[i] * ex2_approx(e) : __int_as_float(0x7FC00000);
+        if (with_status) {
+          const uint32_t st = !nbok[i] ? HB_PAIR_BAD_INPUT
+                                       : (!ok ? HB_PAIR_ZERO_WAVE : (small ? HB_PAIR_SMALL : HB_PAIR_LARGE));
+          st2 |= st << (8 * i);
+        }
+      }
+      store_vec<float, VEC>(p.scaled_ns + base, outv);
+      store_vec<uint32_t, VEC>(p.dest_waves + base, wavv);
+      if (VEC == 2) {
+        *reinterpret_cast<uint16_t*>(p.dest_occ + base) = static_cast<uint16_t>(__byte_perm(occ2, 0u, 0x4420u));
+        if (with_status) *reinterpret_cast<uint16_t*>(p.status + base) = static_cast<uint16_t>(st2);
+      } else {
+        p.dest_occ[base] = static_cast<uint8_t>(occ2);
+        if (with_status) p.status[base] = static_cast<uint8_t>(st2);
+      }
     }
-    store_vec<float, 2>(p.scaled_ns + base, outv);
-    *reinterpret_cast<uint16_t*>(p.dest_occ + base) = static_cast<uint16_t>(__byte_perm(occ2, 0u, 0x4420u));
-    store_vec<uint32_t, 2>(p.dest_waves + base, wavv);
   }
 }
 
-// Finds (or appends) the class of `f` under `same`; returns -1 when full.
-template <typename Same>
-int class_of(FastDev* classes, int32_t* n, const FastDev& f, Same same) {
-  for (int c = 0; c < *n; ++c)
-    if (same(classes[c], f)) return c;
-  if (*n >= kMaxClasses) return -1;
-  classes[*n] = f;
-  return (*n)++;
-}
+// ---------------------------------------------------------------------------
+// Host side: device table, per-GPU upload, launch selection
+// ---------------------------------------------------------------------------
+// The table hb_set_devices receives is kept on the host; every GPU of the process gets its own
+// copy (constant rows, tabulated limits) the first time it is used after a change, so one
+// process may drive several GPUs.  All of it is guarded by one mutex; hb_wave_scale only takes
+// the lock when the current GPU's copy is stale.
+constexpr int kMaxCudaDevices = 64;
 
-bool build_class_params(const FastParams& fp, ClassParams* cp) {
-  std::memset(cp, 0, sizeof(*cp));
-  cp->D = fp.D;
-  cp->K = fp.K;
-  for (int d = -1; d < fp.D; ++d) {
-    const FastDev& f = d < 0 ? fp.origin : fp.dest[d];
-    ClassDev& c = d < 0 ? cp->origin : cp->dest[d];
-    const int rc = class_of(cp->cls_r, &cp->n_rc, f, same_regs_class);
-    const int wc = class_of(cp->cls_w, &cp->n_wc, f, same_warps_class);
-    const int sc = class_of(cp->cls_s, &cp->n_sc, f, same_smem_class);
-    if (rc < 0 || wc < 0 || sc < 0 || f.blocks_limit > 255) return false;
-    c.rc = static_cast<uint8_t>(rc);
-    c.wc = static_cast<uint8_t>(wc);
-    c.sc = static_cast<uint8_t>(sc);
-    c.blocks_limit = static_cast<uint8_t>(f.blocks_limit);
-    c.num_sms = f.num_sms;
-    c.sms_magic = f.sms_magic;
-    c.a_hi = f.a_hi; c.a_lo = f.a_lo; c.b_hi = f.b_hi; c.b_lo = f.b_lo;
-    c.clk_hi = static_cast<float>(f.log2_clk);
-    c.clk_lo = static_cast<float>(f.log2_clk - static_cast<double>(c.clk_hi));
-  }
-  return true;
-}
+struct HostTable {
+  int n = 0;
+  hb_device_spec rows[HB_MAX_DEVICES];
+  hb_dev_pre pre[HB_MAX_DEVICES];
+  bool lut_ok[HB_MAX_DEVICES] = {};
+  uint64_t row_version[HB_MAX_DEVICES] = {};   // bumped when a row's specification changes
+  std::vector<uint8_t> lut_p = std::vector<uint8_t>(static_cast<size_t>(HB_MAX_DEVICES) * kLutP);
+  std::vector<uint8_t> lut_s = std::vector<uint8_t>(static_cast<size_t>(HB_MAX_DEVICES) * kLutS);
+  std::vector<LutOcc> lut_t = std::vector<LutOcc>(static_cast<size_t>(HB_MAX_DEVICES) * kLutOcc);
+};
+struct GpuCopy {
+  bool constants = false;                      // row-independent tables uploaded
+  uint64_t row_version[HB_MAX_DEVICES] = {};   // version of each row this GPU holds
+  int sm_count = 0;
+};
+
+std::mutex g_mu;
+HostTable g_tab;
+GpuCopy g_gpu[kMaxCudaDevices];
+std::atomic<uint64_t> g_version{0};                       // bumped by every hb_set_devices that changed a row
+std::atomic<uint64_t> g_gpu_version[kMaxCudaDevices];     // table version each GPU has seen
 
 // Whether a row can be tabulated for wave_scale_lut_kernel.
 bool lut_row_ok(const hb_device_spec& s, const hb_dev_pre& pre) {
-  return fast_row_ok(s, pre) && s.num_sms >= 16 && s.num_sms * pre.blocks_limit < kWaveMagicN && pre.max_threads_per_block % 32 == 0 &&
+  return fast_row_ok(s, pre) && s.num_sms >= 2 && pre.max_threads_per_block % 32 == 0 &&
          pre.max_threads_per_block <= 1024 && pre.smem_reserved % 128 == 0 &&
-         pre.smem_cap <= (kLutS - 2) * 128 && pre.blocks_limit <= 127;
+         pre.smem_cap <= (kLutS - 2) * 128 && pre.blocks_limit <= kLutOcc - 1 && s.base_clock_mhz > 0;
 }
 
-// Tabulates the three limits of one device row (host side of hb_set_devices).
-void build_row_lut(const FastDev& f, uint8_t* r, uint8_t* w, uint8_t* sm, const uint32_t* magic) {
-  auto clamp = [](int32_t v) { return static_cast<uint8_t>(v < 0 ? 0 : (v > 127 ? 127 : v)); };
+// Tabulates one device row (host side of hb_set_devices).
+void build_row_lut(const hb_device_spec& spec, const FastDev& f, uint8_t* pt, uint8_t* st, LutOcc* tt,
+                   const uint32_t* magic) {
+  auto clamp = [](int32_t v) { return v < 0 ? 0 : (v > 127 ? 127 : v); };
   for (int wpb = 0; wpb < kLutW; ++wpb) {
     FastKernel k{};
-    k.block_size = wpb * 32;
+    k.block_size = wpb * 32;   // the largest block of this many warps; thread limits are multiples of 32
     k.wpb = wpb;
     k.m_wpb = magic_of(static_cast<uint32_t>(wpb));
-    w[wpb] = clamp(fast_warps_limit(f, k));
+    const int32_t lw = clamp(fast_warps_limit(f, k));
     for (int u = 0; u < kLutU; ++u) {
       k.regs = u * 8;          // any count with this many 256-register units per warp
       k.rpw_units = u;
-      r[wpb * kLutU + u] = wpb == 0 ? 0 : clamp(fast_regs_limit(f, k, k.regs, u, magic_of(static_cast<uint32_t>(u))));
+      int32_t v = 0;
+      if (wpb != 0) {
+        v = clamp(fast_regs_limit(f, k, k.regs, u, magic_of(static_cast<uint32_t>(u))));
+        v = v < lw ? v : lw;
+        v = v < f.blocks_limit ? v : f.blocks_limit;
+      }
+      pt[wpb * kLutU + u] = static_cast<uint8_t>(v);
     }
   }
-  for (int i = kLutW; i < kLutWPad; ++i) w[i] = 0;
-  for (int st = 0; st < kLutS; ++st) {
+  for (int s = 0; s < kLutS; ++s) {
     FastKernel k{};
-    k.smem = st * 128;         // the largest request of this 128-byte step
-    sm[st] = st == kLutS - 1 ? 0 : clamp(fast_smem_limit(f, k, magic));
+    k.smem = s * 128;          // the largest request of this 128-byte step
+    st[s] = s == kLutS - 1 ? 0 : static_cast<uint8_t>(clamp(fast_smem_limit(f, k, magic)));
   }
+  const double l_clk = std::log2(static_cast<double>(spec.base_clock_mhz));
+  for (int occ = 0; occ < kLutOcc; ++occ) {
+    LutOcc e{0u, 0u, 0.0f, 0.0f};
+    if (occ > 0) {
+      const uint64_t wave = static_cast<uint64_t>(spec.num_sms) * occ;   // >= 2
+      int s = 0;
+      while ((uint64_t{1} << s) < wave) ++s;                             // ceil(log2 wave) >= 1
+      e.magic = static_cast<uint32_t>((uint64_t{1} << (31 + s)) / wave + 1);
+      e.shift = static_cast<uint32_t>(s - 1);
+      const double a = std::log2(static_cast<double>(occ)) - l_clk;
+      e.lg_hi = static_cast<float>(a);
+      e.lg_lo = static_cast<float>(a - static_cast<double>(e.lg_hi));
+    }
+    tt[occ] = e;
+  }
+}
+
+// Brings the current GPU's copy of the table up to date (rows that changed since its last
+// upload, plus the row-independent tables on first use).  Synchronises the device when it
+// uploads anything, so launches on any stream see the new rows.
+hb_status sync_gpu(int* sm_count) {
+  int dev = 0;
+  HB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxCudaDevices) {
+    hb::set_error("hb_wave_scale: device ordinal %d out of range", dev);
+    return HB_ERR_UNSUPPORTED;
+  }
+  if (g_gpu_version[dev].load(std::memory_order_acquire) == g_version.load(std::memory_order_acquire) &&
+      g_gpu[dev].constants) {
+    if (sm_count) *sm_count = g_gpu[dev].sm_count;
+    return HB_OK;
+  }
+  std::lock_guard<std::mutex> lock(g_mu);
+  GpuCopy& gc = g_gpu[dev];
+  bool uploaded = false;
+  if (!gc.constants) {
+    HB_CUDA_TRY(cudaDeviceGetAttribute(&gc.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    double lg[65];
+    lg[0] = 0.0;
+    for (int i = 1; i <= 64; ++i) lg[i] = std::log2(static_cast<double>(i));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(c_log2_int, lg, sizeof(lg)));
+    uint32_t magic[kMagicN];
+    for (int i = 0; i < kMagicN; ++i) magic[i] = magic_of(static_cast<uint32_t>(i));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_magic, magic, sizeof(magic)));
+    gc.constants = true;
+    uploaded = true;
+  }
+  for (int i = 0; i < g_tab.n; ++i) {
+    if (gc.row_version[i] == g_tab.row_version[i]) continue;
+    HB_CUDA_TRY(cudaMemcpyToSymbol(c_dev, &g_tab.pre[i], sizeof(hb_dev_pre), sizeof(hb_dev_pre) * i));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_p, &g_tab.lut_p[static_cast<size_t>(i) * kLutP], kLutP,
+                                   static_cast<size_t>(i) * kLutP));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_s, &g_tab.lut_s[static_cast<size_t>(i) * kLutS], kLutS,
+                                   static_cast<size_t>(i) * kLutS));
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_t, &g_tab.lut_t[static_cast<size_t>(i) * kLutOcc],
+                                   sizeof(LutOcc) * kLutOcc, sizeof(LutOcc) * kLutOcc * i));
+    gc.row_version[i] = g_tab.row_version[i];
+    uploaded = true;
+  }
+  if (uploaded) HB_CUDA_TRY(cudaDeviceSynchronize());
+  g_gpu_version[dev].store(g_version.load(std::memory_order_acquire), std::memory_order_release);
+  if (sm_count) *sm_count = gc.sm_count;
+  return HB_OK;
 }
 
 uint32_t pair_selector(int c) {
@@ -743,68 +766,136 @@ uint32_t pair_selector(int c) {
   return lo | ((8u | lo) << 4) | (hi << 8) | ((8u | hi) << 12);
 }
 
-// Launches wave_scale_lut_kernel when the launch qualifies; false = nothing launched.
-bool try_launch_lut(const Ptrs& p, const FastParams& fp, const ClassParams& cp, const LaunchParams& lp,
-                    cudaStream_t stream, hb_status* st) {
-  const int64_t K = fp.K;
-  auto al = [](const void* q, uintptr_t a) { return (reinterpret_cast<uintptr_t>(q) & (a - 1)) == 0; };
-  if (K % 2 != 0 || !al(p.num_blocks, 8) || !al(p.smem, 8) || !al(p.time_ns, 8) || !al(p.gamma, 8) ||
-      !al(p.block_size, 4) || !al(p.regs, 4) || !al(p.scaled_ns, 8) || !al(p.dest_waves, 8) ||
-      !al(p.origin_waves, 8) || !al(p.dest_occ, 2) || !al(p.origin_occ, 2))
-    return false;
-  if (static_cast<int64_t>(lp.D) * K >= (int64_t{1} << 31)) return false;   // 32-bit element indices
-  if (!g_lut_ok[lp.origin_row]) return false;
-  for (int d = 0; d < lp.D; ++d)
-    if (!g_lut_ok[lp.dest_row[d]]) return false;
+bool same_p_class(const FastDev& a, const FastDev& b) {
+  return same_regs_class(a, b) && same_warps_class(a, b) && a.blocks_limit == b.blocks_limit;
+}
 
-  LutParams q{};
-  q.D = cp.D; q.K = K; q.n_rc = cp.n_rc; q.n_wc = cp.n_wc; q.n_sc = cp.n_sc;
-  // a class is represented by the first row of the launch that belongs to it
-  bool have_r[kMaxClasses] = {}, have_w[kMaxClasses] = {}, have_s[kMaxClasses] = {};
-  for (int d = -1; d < lp.D; ++d) {
-    const ClassDev& c = d < 0 ? cp.origin : cp.dest[d];
-    const int row = d < 0 ? lp.origin_row : lp.dest_row[d];
-    if (!have_r[c.rc]) { have_r[c.rc] = true; q.row_r[c.rc] = row; }
-    if (!have_w[c.wc]) { have_w[c.wc] = true; q.row_w[c.wc] = row; }
-    if (!have_s[c.sc]) { have_s[c.sc] = true; q.row_s[c.sc] = row; }
-    LutDev& o = d < 0 ? q.origin : q.dest[d];
-    o.num_sms = c.num_sms; o.sms_magic = c.sms_magic;
-    o.a_hi = c.a_hi; o.a_lo = c.a_lo; o.b_hi = c.b_hi; o.b_lo = c.b_lo;
-    o.clk_hi = c.clk_hi; o.clk_lo = c.clk_lo;
-    o.sel_r = pair_selector(c.rc); o.sel_w = pair_selector(c.wc); o.sel_s = pair_selector(c.sc);
-    o.bl2 = static_cast<uint32_t>(c.blocks_limit) * 0x00010001u;
+// Class (index into `rows`, which lists the first row of each class) of `row`; -1 when full.
+template <typename Same>
+int class_of(int* rows, int* n, int row, Same same) {
+  for (int c = 0; c < *n; ++c)
+    if (same(fold_fast(g_tab.rows[rows[c]], g_tab.pre[rows[c]]), fold_fast(g_tab.rows[row], g_tab.pre[row]))) return c;
+  if (*n >= kMaxClasses) return -1;
+  rows[*n] = row;
+  return (*n)++;
+}
+
+template <int VEC, bool EXT, int NP, int NS>
+cudaError_t launch_lut(unsigned grid, cudaStream_t stream, const Ptrs& p, const LutParams& q) {
+  return hb::launch_overlapped(wave_scale_lut_kernel<VEC, EXT, NP, NS>, dim3(grid), dim3(kLutThreads), 0, stream, p, q);
+}
+
+template <int NP>
+cudaError_t launch_lut_plain(int ns, unsigned grid, cudaStream_t stream, const Ptrs& p, const LutParams& q) {
+  switch (ns) {
+    case 1: return launch_lut<2, false, NP, 1>(grid, stream, p, q);
+    case 2: return launch_lut<2, false, NP, 2>(grid, stream, p, q);
+    case 3: return launch_lut<2, false, NP, 3>(grid, stream, p, q);
+    default: return launch_lut<2, false, NP, 4>(grid, stream, p, q);
   }
+}
 
-  const int64_t blocks = (K / 2 + kLutThreads - 1) / kLutThreads;
-  if (blocks > 0x7FFFFFFF || blocks < 1) return false;
-  const unsigned grid = static_cast<unsigned>(blocks);
-  // 12 blocks of 128 threads per SM (40 registers) measured fastest; 8, 10 and 16 were slower
-  const cudaError_t le = hb::launch_overlapped(wave_scale_lut_kernel, dim3(grid), dim3(kLutThreads), 0, stream, p, q);
+// Launches wave_scale_lut_kernel when the launch qualifies; false = nothing launched.
+bool try_launch_lut(const Ptrs& p, const LaunchParams& lp, int sm_count, cudaStream_t stream, hb_status* st) {
+  static const bool use_lut = [] { const char* e = std::getenv("HB_WAVE_LUT"); return !e || std::atoi(e) != 0; }();
+  if (!use_lut || p.limits || lp.D > HB_MAX_DEVICES / 2) return false;
+  const int64_t K = lp.K;
+  if (static_cast<int64_t>(lp.D) * K >= (int64_t{1} << 31)) return false;   // 32-bit element indices
+  LutParams q{};
+  int rows_p[kMaxClasses] = {}, rows_s[kMaxClasses] = {}, n_p = 0, n_s = 0;
+  bool many_classes = false;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!g_tab.lut_ok[lp.origin_row]) return false;
+    for (int d = 0; d < lp.D; ++d)
+      if (!g_tab.lut_ok[lp.dest_row[d]]) return false;
+    for (int d = -1; d < lp.D; ++d) {
+      const int row = d < 0 ? lp.origin_row : lp.dest_row[d];
+      const int pc = many_classes ? -1 : class_of(rows_p, &n_p, row, same_p_class);
+      const int sc = many_classes ? -1 : class_of(rows_s, &n_s, row, same_smem_class);
+      if (pc < 0 || sc < 0) many_classes = true;   // more than four classes: every row's own tables (extended variant)
+      LutDev& o = d < 0 ? q.origin : q.dest[d];
+      o.sel_p = pair_selector(pc < 0 ? 0 : pc);
+      o.sel_s = pair_selector(sc < 0 ? 0 : sc);
+      o.t_off = static_cast<uint32_t>(row * kLutOcc * sizeof(LutOcc));
+      o.p_off = static_cast<uint32_t>(row * kLutP);
+      o.s_off = static_cast<uint32_t>(row * kLutS);
+      o.sms_m1 = static_cast<uint32_t>(g_tab.rows[row].num_sms - 1);
+      o.sms_magic = magic_of(static_cast<uint32_t>(g_tab.rows[row].num_sms));
+      if (d >= 0) {
+        o.a_hi = static_cast<float>(lp.a[d]);
+        o.a_lo = static_cast<float>(lp.a[d] - static_cast<double>(o.a_hi));
+        o.b_hi = static_cast<float>(lp.b[d]);
+        o.b_lo = static_cast<float>(lp.b[d] - static_cast<double>(o.b_hi));
+        q.ridge[d] = lp.ridge[d];
+        q.slope[d] = -0.5 / lp.ridge[d];
+      }
+    }
+  }
+  // class slots beyond the count repeat class 0 (the kernel variants are built for 1..4 classes,
+  // the extended one always loads four)
+  for (int c = 0; c < kMaxClasses; ++c) {
+    q.off_p[c] = static_cast<uint32_t>(rows_p[c < n_p ? c : 0] * kLutP);   // unused by the extended variant
+    q.off_s[c] = static_cast<uint32_t>(rows_s[c < n_s ? c : 0] * kLutS);
+  }
+  q.K = static_cast<uint32_t>(K);
+  q.D = lp.D;
+  q.origin_peak = lp.origin_peak;
+
+  auto al = [](const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; };
+  const bool metrics = p.has_metrics != nullptr;
+  const bool ext = metrics || p.dest_regs != nullptr || p.status != nullptr || many_classes;
+  const bool vec2 = K % 2 == 0 && al(p.num_blocks, 8) && al(p.smem, 8) && al(p.time_ns, 8) &&
+                    (metrics || al(p.gamma, 8)) && al(p.block_size, 4) && al(p.regs, 4) && al(p.scaled_ns, 8) &&
+                    al(p.dest_waves, 8) && al(p.origin_waves, 8) && al(p.dest_occ, 2) && al(p.origin_occ, 2) &&
+                    (!p.status || al(p.status, 2)) && (!p.dest_regs || al(p.dest_regs, 4));
+  const int vec = vec2 ? 2 : 1;
+  const int64_t blocks = ((K + vec - 1) / vec + kLutThreads - 1) / kLutThreads;
+  // persistent grid: at most HB_LUT_BLOCKS_PER_SM resident blocks per SM stride over the batch
+  static const int per_sm = [] { const char* e = std::getenv("HB_LUT_BLOCKS_PER_SM"); return e ? std::atoi(e) : 12; }();
+  const int64_t cap = per_sm > 0 ? static_cast<int64_t>(sm_count) * (ext ? (per_sm < 8 ? per_sm : 8) : per_sm) : blocks;
+  const unsigned grid = static_cast<unsigned>(blocks < cap ? blocks : cap);
+  cudaError_t le;
+  if (ext) {
+    le = vec2 ? launch_lut<2, true, 1, 1>(grid, stream, p, q) : launch_lut<1, true, 1, 1>(grid, stream, p, q);
+  } else if (!vec2) {
+    le = launch_lut<1, false, 4, 4>(grid, stream, p, q);
+  } else {
+    switch (n_p) {
+      case 1: le = launch_lut_plain<1>(n_s, grid, stream, p, q); break;
+      case 2: le = launch_lut_plain<2>(n_s, grid, stream, p, q); break;
+      case 3: le = launch_lut_plain<3>(n_s, grid, stream, p, q); break;
+      default: le = launch_lut_plain<4>(n_s, grid, stream, p, q); break;
+    }
+  }
   t_path = 4;
   const cudaError_t ce = le != cudaSuccess ? le : cudaGetLastError();
   *st = ce == cudaSuccess ? HB_OK : hb::cuda_fail(ce, "wave_scale_lut_kernel launch");
   return true;
 }
 
-// Fast path when every row of the launch qualifies and only the five standard
+// Division-free kernel when every row of the launch is ordinary and only the five standard
 // outputs are wanted; returns false (nothing launched) otherwise.
 bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream, hb_status* st) {
   if (p.status || p.limits || lp.D > HB_MAX_DEVICES / 2) return false;
-  if (!fast_row_ok(g_rows[lp.origin_row], g_pre[lp.origin_row])) return false;
-  for (int d = 0; d < lp.D; ++d)
-    if (!fast_row_ok(g_rows[lp.dest_row[d]], g_pre[lp.dest_row[d]])) return false;
   FastParams fp{};
-  fp.D = lp.D;
-  fp.K = lp.K;
-  fp.origin = fold_fast(g_rows[lp.origin_row], g_pre[lp.origin_row]);
-  for (int d = 0; d < lp.D; ++d) {
-    FastDev& f = fp.dest[d];
-    f = fold_fast(g_rows[lp.dest_row[d]], g_pre[lp.dest_row[d]]);
-    f.a_hi = static_cast<float>(lp.a[d]);
-    f.a_lo = static_cast<float>(lp.a[d] - static_cast<double>(f.a_hi));
-    f.b_hi = static_cast<float>(lp.b[d]);
-    f.b_lo = static_cast<float>(lp.b[d] - static_cast<double>(f.b_hi));
-    f.log2_clk = lp.log2_clk[d];
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!fast_row_ok(g_tab.rows[lp.origin_row], g_tab.pre[lp.origin_row])) return false;
+    for (int d = 0; d < lp.D; ++d)
+      if (!fast_row_ok(g_tab.rows[lp.dest_row[d]], g_tab.pre[lp.dest_row[d]])) return false;
+    fp.D = lp.D;
+    fp.K = lp.K;
+    fp.origin = fold_fast(g_tab.rows[lp.origin_row], g_tab.pre[lp.origin_row]);
+    for (int d = 0; d < lp.D; ++d) {
+      FastDev& f = fp.dest[d];
+      f = fold_fast(g_tab.rows[lp.dest_row[d]], g_tab.pre[lp.dest_row[d]]);
+      f.a_hi = static_cast<float>(lp.a[d]);
+      f.a_lo = static_cast<float>(lp.a[d] - static_cast<double>(f.a_hi));
+      f.b_hi = static_cast<float>(lp.b[d]);
+      f.b_lo = static_cast<float>(lp.b[d] - static_cast<double>(f.b_hi));
+      f.log2_clk = lp.log2_clk[d];
+    }
   }
   const int64_t K = lp.K;
   const bool vec4 = vec4_ok(p, K, true);
@@ -814,25 +905,6 @@ bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream,
     hb::set_error("hb_wave_scale: K too large for one launch");
     *st = HB_ERR_TOO_LARGE;
     return true;
-  }
-  ClassParams cp;
-  if (!p.dest_regs && build_class_params(fp, &cp)) {
-    static const bool use_lut = [] { const char* e = std::getenv("HB_WAVE_LUT"); return !e || std::atoi(e) != 0; }();
-    if (use_lut && try_launch_lut(p, fp, cp, lp, stream, st)) return true;
-    const int cthreads = 128;
-    static const int vec_pref = [] { const char* e = std::getenv("HB_WAVE_VEC"); return e ? std::atoi(e) : 2; }();
-    // two records per thread measured fastest (more resident warps than four per thread)
-    const int cvec = vec4 ? (vec_pref == 4 ? 4 : (vec_pref == 1 ? 1 : 2)) : 1;
-    const int64_t cblocks = ((K + cvec - 1) / cvec + cthreads - 1) / cthreads;
-    if (cblocks <= 0x7FFFFFFF) {
-      if (cvec == 4) wave_scale_class_kernel<4><<<static_cast<unsigned>(cblocks), cthreads, 0, stream>>>(p, cp);
-      else if (cvec == 2) wave_scale_class_kernel<2><<<static_cast<unsigned>(cblocks), cthreads, 0, stream>>>(p, cp);
-      else wave_scale_class_kernel<1><<<static_cast<unsigned>(cblocks), cthreads, 0, stream>>>(p, cp);
-      t_path = 3;
-      const cudaError_t ce = cudaGetLastError();
-      *st = ce == cudaSuccess ? HB_OK : hb::cuda_fail(ce, "wave_scale_class_kernel launch");
-      return true;
-    }
   }
   const dim3 grid(static_cast<unsigned>(blocks));
   if (vec4) {
@@ -850,12 +922,14 @@ bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream,
 
 template <bool METRICS>
 hb_status launch(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream) {
+  int sm_count = 0;
+  const hb_status sync_st = sync_gpu(&sm_count);
+  if (sync_st != HB_OK) return sync_st;
   const int64_t K = lp.K;
   const bool extra = p.status != nullptr || p.limits != nullptr;
-  if (!METRICS) {
-    hb_status fast_st = HB_OK;
-    if (try_launch_fast(p, lp, stream, &fast_st)) return fast_st;
-  }
+  hb_status fast_st = HB_OK;
+  if (try_launch_lut(p, lp, sm_count, stream, &fast_st)) return fast_st;
+  if (!METRICS && try_launch_fast(p, lp, stream, &fast_st)) return fast_st;
   const bool vec4 = vec4_ok(p, K, !METRICS);
   const int threads = 256;
   const int vec = vec4 ? 4 : 1;
@@ -880,12 +954,13 @@ hb_status launch(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream) {
 
 hb_status fill_params(LaunchParams* lp, int64_t K, int32_t origin_row, const int32_t* dest_rows,
                       int32_t D) {
-  if (g_n_rows == 0) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (g_tab.n == 0) {
     hb::set_error("hb_wave_scale: no device table (call hb_set_devices first)");
     return HB_ERR_INVALID_ARGUMENT;
   }
   if (K < 0 || D < 1 || D > HB_MAX_DEVICES || !dest_rows || origin_row < 0 ||
-      origin_row >= g_n_rows) {
+      origin_row >= g_tab.n) {
     hb::set_error("hb_wave_scale: bad K/D/origin_row");
     return HB_ERR_INVALID_ARGUMENT;
   }
@@ -893,15 +968,15 @@ hb_status fill_params(LaunchParams* lp, int64_t K, int32_t origin_row, const int
   lp->D = D;
   lp->K = K;
   lp->origin_row = origin_row;
-  const hb_device_spec& o = g_rows[origin_row];
+  const hb_device_spec& o = g_tab.rows[origin_row];
   lp->origin_peak = static_cast<double>(o.peak_gflops_per_second);
   for (int d = 0; d < D; ++d) {
     const int r = dest_rows[d];
-    if (r < 0 || r >= g_n_rows) {
+    if (r < 0 || r >= g_tab.n) {
       hb::set_error("hb_wave_scale: destination row %d out of range", r);
       return HB_ERR_INVALID_ARGUMENT;
     }
-    const hb_device_spec& t = g_rows[r];
+    const hb_device_spec& t = g_tab.rows[r];
     lp->dest_row[d] = static_cast<uint8_t>(r);
     // wave_scaling/roofline.py:48-57: ratios of the integer device fields
     const double l_bw = std::log2(static_cast<double>(o.mem_bandwidth_gb) / t.mem_bandwidth_gb);
@@ -967,55 +1042,45 @@ extern "C" hb_status hb_set_devices(const hb_device_spec* rows, int32_t n) {
       hb::set_error("hb_set_devices: row %d has a non-positive bandwidth/clock/SM/peak field", i);
       return HB_ERR_INVALID_ARGUMENT;
     }
-    g_rows[i] = rows[i];
-    g_pre[i] = hb_fold_device(rows[i]);
   }
-  g_n_rows = n;
-  HB_CUDA_TRY(cudaMemcpyToSymbol(c_dev, g_pre, sizeof(hb_dev_pre) * n));
-  double lg[65];
-  lg[0] = 0.0;
-  for (int i = 1; i <= 64; ++i) lg[i] = std::log2(static_cast<double>(i));
-  HB_CUDA_TRY(cudaMemcpyToSymbol(c_log2_int, lg, sizeof(lg)));
-  uint32_t magic[kMagicN];
-  for (int i = 0; i < kMagicN; ++i) magic[i] = magic_of(static_cast<uint32_t>(i));
-  HB_CUDA_TRY(cudaMemcpyToSymbol(g_magic, magic, sizeof(magic)));
   {
-    // Host copies of the tables persist between calls: a row is tabulated again only when its
-    // specification changed (callers append rows one at a time and upload the whole table).
-    static std::vector<uint8_t> r(static_cast<size_t>(HB_MAX_DEVICES) * kLutW * kLutU),
-        w(static_cast<size_t>(HB_MAX_DEVICES) * kLutWPad), sm(static_cast<size_t>(HB_MAX_DEVICES) * kLutS);
-    static hb_device_spec built[HB_MAX_DEVICES];
-    static bool have[HB_MAX_DEVICES] = {};
+    std::lock_guard<std::mutex> lock(g_mu);
+    uint32_t magic[kMagicN];
+    for (int i = 0; i < kMagicN; ++i) magic[i] = magic_of(static_cast<uint32_t>(i));
+    bool changed = n != g_tab.n;
     for (int i = 0; i < n; ++i) {
-      if (have[i] && std::memcmp(&built[i], &g_rows[i], sizeof(hb_device_spec)) == 0) continue;
-      built[i] = g_rows[i];
-      have[i] = true;
-      g_lut_ok[i] = lut_row_ok(g_rows[i], g_pre[i]);
-      uint8_t* ri = &r[static_cast<size_t>(i) * kLutW * kLutU];
-      uint8_t* wi = &w[static_cast<size_t>(i) * kLutWPad];
-      uint8_t* si = &sm[static_cast<size_t>(i) * kLutS];
-      if (g_lut_ok[i]) {
-        build_row_lut(fold_fast(g_rows[i], g_pre[i]), ri, wi, si, magic);
+      // a row is folded and tabulated again only when its specification changed (callers append
+      // rows one at a time and pass the whole table); rows already on a GPU are left alone
+      if (i < g_tab.n && g_tab.row_version[i] != 0 &&
+          std::memcmp(&g_tab.rows[i], &rows[i], sizeof(hb_device_spec)) == 0)
+        continue;
+      g_tab.rows[i] = rows[i];
+      g_tab.pre[i] = hb_fold_device(rows[i]);
+      g_tab.lut_ok[i] = lut_row_ok(g_tab.rows[i], g_tab.pre[i]);
+      uint8_t* pt = &g_tab.lut_p[static_cast<size_t>(i) * kLutP];
+      uint8_t* st = &g_tab.lut_s[static_cast<size_t>(i) * kLutS];
+      LutOcc* tt = &g_tab.lut_t[static_cast<size_t>(i) * kLutOcc];
+      if (g_tab.lut_ok[i]) {
+        build_row_lut(g_tab.rows[i], fold_fast(g_tab.rows[i], g_tab.pre[i]), pt, st, tt, magic);
       } else {
-        std::memset(ri, 0, kLutW * kLutU);
-        std::memset(wi, 0, kLutWPad);
-        std::memset(si, 0, kLutS);
+        std::memset(pt, 0, kLutP);
+        std::memset(st, 0, kLutS);
+        std::memset(tt, 0, sizeof(LutOcc) * kLutOcc);
       }
+      ++g_tab.row_version[i];
+      changed = true;
     }
-    float2 lp2[33];
-    for (int i = 0; i < 33; ++i) {
-      const float hi = static_cast<float>(lg[i]);
-      lp2[i] = make_float2(hi, static_cast<float>(lg[i] - static_cast<double>(hi)));
-    }
-    HB_CUDA_TRY(cudaMemcpyToSymbol(g_log2_pair, lp2, sizeof(lp2)));
-    std::vector<uint32_t> wm(kWaveMagicN);
-    for (int i = 0; i < kWaveMagicN; ++i) wm[i] = magic_of(static_cast<uint32_t>(i));
-    HB_CUDA_TRY(cudaMemcpyToSymbol(g_wave_magic, wm.data(), wm.size() * sizeof(uint32_t)));
-    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_r, r.data(), static_cast<size_t>(n) * kLutW * kLutU));
-    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_w, w.data(), static_cast<size_t>(n) * kLutWPad));
-    HB_CUDA_TRY(cudaMemcpyToSymbol(g_lut_s, sm.data(), static_cast<size_t>(n) * kLutS));
+    g_tab.n = n;
+    if (changed) g_version.fetch_add(1, std::memory_order_acq_rel);
   }
-  return HB_OK;
+  // the current GPU gets its copy now; the others on their first launch.  A process without a
+  // GPU keeps the host table only (hb_thread_block_occupancy needs no more).
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+    cudaGetLastError();   // not an error of this call
+    return HB_OK;
+  }
+  return sync_gpu(nullptr);
 }
 
 extern "C" hb_status hb_wave_scale(const hb_kernel_soa* kernels, int64_t K, int32_t origin_row,
@@ -1052,18 +1117,6 @@ extern "C" hb_status hb_wave_scale_metrics(const hb_kernel_soa* kernels,
                       static_cast<cudaStream_t>(stream));
 }
 
-namespace {
-
-// Scoped device buffer for the host-buffer entry points.
-struct DevBuf {
-  void* p = nullptr;
-  ~DevBuf() { if (p) cudaFree(p); }
-  cudaError_t alloc(size_t n) { return cudaMalloc(&p, n ? n : 1); }
-  template <typename T> T* as() { return static_cast<T*>(p); }
-};
-
-}  // namespace
-
 extern "C" hb_status hb_wave_scale_host(const hb_kernel_soa* kernels, int64_t K,
                                         int32_t origin_row, const int32_t* dest_rows_host,
                                         int32_t D, const int16_t* dest_regs,
@@ -1075,43 +1128,62 @@ extern "C" hb_status hb_wave_scale_host(const hb_kernel_soa* kernels, int64_t K,
   if (st != HB_OK) return st;
   if (K == 0) return HB_OK;
   const size_t k = static_cast<size_t>(K), kd = k * D;
-  cudaStream_t s = nullptr;
-  DevBuf nb, bs, rg, sm, tm, gm, dr, o_ns, o_occ, o_wav, o_oocc, o_owav, o_st, o_lim;
-  HB_CUDA_TRY(nb.alloc(k * 4)); HB_CUDA_TRY(bs.alloc(k * 2)); HB_CUDA_TRY(rg.alloc(k * 2));
-  HB_CUDA_TRY(sm.alloc(k * 4)); HB_CUDA_TRY(tm.alloc(k * 4)); HB_CUDA_TRY(gm.alloc(k * 4));
-  HB_CUDA_TRY(o_ns.alloc(kd * 4)); HB_CUDA_TRY(o_occ.alloc(kd)); HB_CUDA_TRY(o_wav.alloc(kd * 4));
-  HB_CUDA_TRY(o_oocc.alloc(k)); HB_CUDA_TRY(o_owav.alloc(k * 4));
-  if (dest_regs) HB_CUDA_TRY(dr.alloc(kd * 2));
-  if (out->status) HB_CUDA_TRY(o_st.alloc(kd));
-  if (out->limits) HB_CUDA_TRY(o_lim.alloc(static_cast<size_t>(D + 1) * 4 * k * 4));
-  const cudaMemcpyKind h2d = cudaMemcpyHostToDevice, d2h = cudaMemcpyDeviceToHost;
-  HB_CUDA_TRY(cudaMemcpyAsync(nb.p, kernels->num_blocks, k * 4, h2d, s));
-  HB_CUDA_TRY(cudaMemcpyAsync(bs.p, kernels->block_size, k * 2, h2d, s));
-  HB_CUDA_TRY(cudaMemcpyAsync(rg.p, kernels->regs_per_thread, k * 2, h2d, s));
-  HB_CUDA_TRY(cudaMemcpyAsync(sm.p, kernels->smem_bytes, k * 4, h2d, s));
-  HB_CUDA_TRY(cudaMemcpyAsync(tm.p, kernels->run_time_ns, k * 4, h2d, s));
-  HB_CUDA_TRY(cudaMemcpyAsync(gm.p, kernels->gamma, k * 4, h2d, s));
-  if (dest_regs) HB_CUDA_TRY(cudaMemcpyAsync(dr.p, dest_regs, kd * 2, h2d, s));
-  hb_kernel_soa dk{nb.as<int32_t>(), bs.as<uint16_t>(), rg.as<uint16_t>(), sm.as<uint32_t>(),
-                   tm.as<float>(), gm.as<float>()};
-  hb_wave_out dout{o_ns.as<float>(), o_occ.as<uint8_t>(), o_wav.as<uint32_t>(),
-                   o_oocc.as<uint8_t>(), o_owav.as<uint32_t>(),
-                   out->status ? o_st.as<uint8_t>() : nullptr,
-                   out->limits ? o_lim.as<int32_t>() : nullptr};
-  st = launch<false>(make_ptrs(&dk, nullptr, dest_regs ? dr.as<int16_t>() : nullptr, &dout), lp, s);
+  // one staging block per GPU, kept between calls, and the library's own stream
+  hb::HostArena* arena = nullptr;
+  st = hb::arena_for_current_device(&arena);
   if (st != HB_OK) return st;
-  HB_CUDA_TRY(cudaMemcpyAsync(out->scaled_ns, o_ns.p, kd * 4, d2h, s));
-  HB_CUDA_TRY(cudaMemcpyAsync(out->dest_occupancy, o_occ.p, kd, d2h, s));
-  HB_CUDA_TRY(cudaMemcpyAsync(out->dest_waves, o_wav.p, kd * 4, d2h, s));
-  HB_CUDA_TRY(cudaMemcpyAsync(out->origin_occupancy, o_oocc.p, k, d2h, s));
-  HB_CUDA_TRY(cudaMemcpyAsync(out->origin_waves, o_owav.p, k * 4, d2h, s));
-  if (out->status) HB_CUDA_TRY(cudaMemcpyAsync(out->status, o_st.p, kd, d2h, s));
-  if (out->limits)
-    HB_CUDA_TRY(cudaMemcpyAsync(out->limits, o_lim.p, static_cast<size_t>(D + 1) * 4 * k * 4, d2h, s));
+  std::lock_guard<std::mutex> lock(arena->mu);
+  const size_t lim_bytes = out->limits ? static_cast<size_t>(D + 1) * 4 * k * 4 : 0;
+  hb::Carver sizes(nullptr);
+  sizes.take<uint8_t>(k * 4); sizes.take<uint8_t>(k * 2); sizes.take<uint8_t>(k * 2); sizes.take<uint8_t>(k * 4);
+  sizes.take<uint8_t>(k * 4); sizes.take<uint8_t>(k * 4); sizes.take<uint8_t>(kd * 4); sizes.take<uint8_t>(kd);
+  sizes.take<uint8_t>(kd * 4); sizes.take<uint8_t>(k); sizes.take<uint8_t>(k * 4); sizes.take<uint8_t>(kd * 2);
+  sizes.take<uint8_t>(kd); sizes.take<uint8_t>(lim_bytes);
+  st = hb::arena_reserve(arena, sizes.used());
+  if (st != HB_OK) return st;
+  hb::Carver c(arena->base);
+  int32_t* nb = c.take<int32_t>(k);
+  uint16_t* bs = c.take<uint16_t>(k);
+  uint16_t* rg = c.take<uint16_t>(k);
+  uint32_t* sm = c.take<uint32_t>(k);
+  float* tm = c.take<float>(k);
+  float* gm = c.take<float>(k);
+  float* o_ns = c.take<float>(kd);
+  uint8_t* o_occ = c.take<uint8_t>(kd);
+  uint32_t* o_wav = c.take<uint32_t>(kd);
+  uint8_t* o_oocc = c.take<uint8_t>(k);
+  uint32_t* o_owav = c.take<uint32_t>(k);
+  int16_t* dr = c.take<int16_t>(kd);
+  uint8_t* o_st = c.take<uint8_t>(kd);
+  int32_t* o_lim = reinterpret_cast<int32_t*>(c.take<uint8_t>(lim_bytes));
+  cudaStream_t s = arena->stream;
+  const cudaMemcpyKind h2d = cudaMemcpyHostToDevice, d2h = cudaMemcpyDeviceToHost;
+  HB_CUDA_TRY(cudaMemcpyAsync(nb, kernels->num_blocks, k * 4, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(bs, kernels->block_size, k * 2, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(rg, kernels->regs_per_thread, k * 2, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(sm, kernels->smem_bytes, k * 4, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(tm, kernels->run_time_ns, k * 4, h2d, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(gm, kernels->gamma, k * 4, h2d, s));
+  if (dest_regs) HB_CUDA_TRY(cudaMemcpyAsync(dr, dest_regs, kd * 2, h2d, s));
+  hb_kernel_soa dk{nb, bs, rg, sm, tm, gm};
+  hb_wave_out dout{o_ns, o_occ, o_wav, o_oocc, o_owav, out->status ? o_st : nullptr,
+                   out->limits ? o_lim : nullptr};
+  st = launch<false>(make_ptrs(&dk, nullptr, dest_regs ? dr : nullptr, &dout), lp, s);
+  if (st != HB_OK) return st;
+  HB_CUDA_TRY(cudaMemcpyAsync(out->scaled_ns, o_ns, kd * 4, d2h, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(out->dest_occupancy, o_occ, kd, d2h, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(out->dest_waves, o_wav, kd * 4, d2h, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(out->origin_occupancy, o_oocc, k, d2h, s));
+  HB_CUDA_TRY(cudaMemcpyAsync(out->origin_waves, o_owav, k * 4, d2h, s));
+  if (out->status) HB_CUDA_TRY(cudaMemcpyAsync(out->status, o_st, kd, d2h, s));
+  if (out->limits) HB_CUDA_TRY(cudaMemcpyAsync(out->limits, o_lim, lim_bytes, d2h, s));
   HB_CUDA_TRY(cudaStreamSynchronize(s));
   return HB_OK;
 }
 
+// The occupancy rules are plain integer code that also compiles for the host
+// (occupancy.cuh), so a single record needs no GPU: no allocation, no launch, no
+// synchronisation, and the call is legal during a stream capture.
 extern "C" hb_status hb_thread_block_occupancy(int32_t device_row, int32_t block_size,
                                                uint32_t smem_bytes, int32_t regs_per_thread,
                                                int32_t* occupancy, int32_t limits[4]) {
@@ -1120,20 +1192,33 @@ extern "C" hb_status hb_thread_block_occupancy(int32_t device_row, int32_t block
     hb::set_error("hb_thread_block_occupancy: argument out of range");
     return HB_ERR_INVALID_ARGUMENT;
   }
-  // One record through the batched kernel, with the queried row as origin.
-  int32_t nb = 1;
-  uint16_t bs = static_cast<uint16_t>(block_size), rg = static_cast<uint16_t>(regs_per_thread);
-  float t = 1.0f, g = 1.0f;
-  hb_kernel_soa k{&nb, &bs, &rg, &smem_bytes, &t, &g};
-  float ns;
-  uint8_t docc, oocc;
-  uint32_t dw, ow;
-  int32_t lim[8];
-  hb_wave_out out{&ns, &docc, &dw, &oocc, &ow, nullptr, lim};
-  const int32_t dest = device_row;
-  hb_status st = hb_wave_scale_host(&k, 1, device_row, &dest, 1, nullptr, &out);
-  if (st != HB_OK) return st;
-  *occupancy = oocc;
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (device_row < 0 || device_row >= g_tab.n) {
+    hb::set_error("hb_thread_block_occupancy: device row %d is not in the table (hb_set_devices)", device_row);
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  int32_t lim[4];
+  const int32_t smem = smem_bytes > 0x7FFF0000u ? -1 : static_cast<int32_t>(smem_bytes);
+  *occupancy = hb_occupancy(g_tab.pre[device_row], block_size, smem, regs_per_thread, lim);
   if (limits) for (int j = 0; j < 4; ++j) limits[j] = lim[j];
   return HB_OK;
 }
+
+#if defined(HB_BOUNDS_CHECK)
+extern "C" hb_status hb_bounds_check_word(uint32_t* word, int32_t reset) {
+  if (!word) return HB_ERR_INVALID_ARGUMENT;
+  HB_CUDA_TRY(cudaDeviceSynchronize());
+  HB_CUDA_TRY(cudaMemcpyFromSymbol(word, g_bounds_word, sizeof(uint32_t)));
+  if (reset) {
+    const uint32_t zero = 0;
+    HB_CUDA_TRY(cudaMemcpyToSymbol(g_bounds_word, &zero, sizeof(uint32_t)));
+  }
+  return HB_OK;
+}
+#else
+extern "C" hb_status hb_bounds_check_word(uint32_t* word, int32_t reset) {
+  (void)word; (void)reset;
+  hb::set_error("hb_bounds_check_word: this build has no index checks (build with -DHB_BOUNDS_CHECK)");
+  return HB_ERR_UNSUPPORTED;
+}
+#endif

@@ -41,7 +41,9 @@ def load_device_file(path=None):
 def _sync():
     global _uploaded, _uploaded_device
     import torch
-    dev = torch.cuda.current_device()
+    # every GPU of the process gets its own copy inside the library (at its first launch after a
+    # change); without a GPU the table still serves the host-side occupancy call
+    dev = torch.cuda.current_device() if torch.cuda.is_available() else -1
     if _uploaded == len(_rows) and _uploaded_device == dev:
         return
     lib = _native.load()

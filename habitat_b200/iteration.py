@@ -35,13 +35,14 @@ def predict_iteration_totals(kernels: batched.KernelBatch, overhead_ns: torch.Te
                              origin, dests: Sequence, origin_mlp_row: int,
                              dest_mlp_rows: Sequence[int]):
     """-> ([I, D] float64 CUDA tensor of predicted ms per iteration and destination,
-    [D, K] uint8 status planes of the wave-scaled kernels).
+    the batched.WaveResult of the wave-scaled kernels: its scaled_ns is NaN for the pairs the
+    reference would raise ZeroDivisionError on, and so are the totals of their iterations).
 
     A destination with the origin's name keeps the measured times, as
     MeasuredOperation.to_device does (analysis/operation.py:82-85)."""
     I = kernel_offsets.numel() - 1
     D = len(dests)
-    res = batched.wave_scale(kernels, origin, dests, want_status=True)
+    res = batched.wave_scale(kernels, origin, dests)
     # sum over kernels of (overhead + scaled) = sum(overhead) + sum(scaled): linear, so the
     # two segment sums replace a per-kernel add
     over = batched.segment_sum(overhead_ns, kernel_offsets)                       # [I]
@@ -72,4 +73,4 @@ def predict_iteration_totals(kernels: batched.KernelBatch, overhead_ns: torch.Te
             else:
                 totals[:, d] += batched.segment_sum(ms[t].contiguous(), ops.offsets)
                 t += 1
-    return totals, res.status
+    return totals, res

@@ -68,8 +68,15 @@ typedef struct {
 
 /* Replaces the per-call `hc.DeviceProperties` arguments of
  * KernelInstance.thread_block_occupancy (cpp/src/frontend/model_bindings.cpp:75-82):
- * rows are uploaded once to constant memory of the current CUDA device and
- * referred to by index afterwards.  n <= HB_MAX_DEVICES.  Synchronous. */
+ * rows are referred to by index afterwards.  n <= HB_MAX_DEVICES.
+ * The table is kept on the host and copied to a GPU (constant rows plus the
+ * tabulated limits of each row) when that GPU is current in this call or in the
+ * first hb_wave_scale after it; only rows whose specification changed are
+ * written again, and the copy ends with a device synchronise, so launches on any
+ * stream see it.  That copy is a set-up step: make it (on every GPU used) before
+ * a stream capture begins.  A row that kernels in flight are reading must not be
+ * given a new specification.  Calls may come from several threads (one mutex
+ * guards the table). */
 hb_status hb_set_devices(const hb_device_spec* rows, int32_t n);
 
 /* Fills a device-table row for CUDA device `device` from the driver's attributes: the eleven
@@ -159,21 +166,26 @@ hb_status hb_wave_scale_metrics(const hb_kernel_soa* kernels, const hb_kernel_me
                                 void* stream);
 
 /* Which kernel the calling thread's most recent hb_wave_scale / hb_wave_scale_metrics call
- * launched: 0 none yet, 1 generic (any device row, status / limits / metrics outputs),
- * 2 division-free, 3 per-limit device classes, 4 tabulated limits.  For tests and for
- * naming the measured kernel; no reference counterpart. */
+ * launched: 0 none yet, 1 generic (any device row, block-limit planes, more than 32
+ * destinations), 2 division-free (ordinary rows that cannot be tabulated), 4 tabulated
+ * limits (status plane, per-destination registers and metrics included).  For tests and
+ * for naming the measured kernel; no reference counterpart. */
 int32_t hb_wave_scale_path(void);
 
 /* Host-buffer form of hb_wave_scale: all pointers in `kernels`, `dest_regs`
- * and `out` are HOST pointers; transfers happen inside the call. */
+ * and `out` are HOST pointers; transfers happen inside the call, through a
+ * staging block and a stream the library keeps per GPU (the block grows when a
+ * larger batch arrives and is never shrunk; `_host` calls on one GPU run one
+ * after the other). */
 hb_status hb_wave_scale_host(const hb_kernel_soa* kernels, int64_t K, int32_t origin_row,
                              const int32_t* dest_rows_host, int32_t D,
                              const int16_t* dest_regs, const hb_wave_out* out);
 
-/* Single-kernel occupancy with the four block limits: the batched device
- * path run on one record.  Stands in for
+/* Single-kernel occupancy with the four block limits.  Stands in for
  * KernelInstance.thread_block_occupancy(device, registers_per_thread)
- * (cpp/src/frontend/model_bindings.cpp:75-82).  Host in/out, synchronous. */
+ * (cpp/src/frontend/model_bindings.cpp:75-82).  Evaluated on the host with the
+ * same integer code the kernels run (as the reference evaluates its header on
+ * the host): no allocation, no launch, no synchronisation. */
 hb_status hb_thread_block_occupancy(int32_t device_row, int32_t block_size, uint32_t smem_bytes,
                                     int32_t regs_per_thread, int32_t* occupancy,
                                     int32_t limits[4]);
@@ -207,15 +219,23 @@ void hb_mlp_destroy(hb_mlp* handle);
 
 /* Replaces RuntimePredictor.predict (analysis/mlp/mlp.py:252-267) for Q
  * queries at once: op_features [Q][F] float32 row-major, device_row [Q]
- * indexes device_features, out [Q] float32 (milliseconds, un-clamped). */
+ * indexes device_features, out [Q] float32 (milliseconds, un-clamped).
+ * The GPU the handle was created on must be current
+ * (HB_ERR_INVALID_ARGUMENT otherwise). */
 hb_status hb_mlp_predict(hb_mlp* handle, const float* op_features, const uint8_t* device_row,
                          int64_t Q, float* out, void* stream);
 
 /* Synchronises with the device and reports whether any launch on this handle
  * gave up on a bounded device-side wait (HB_ERR_DEVICE_TIMEOUT; *device_status
- * names the waiting role and site) since the handle was created.  No reference
- * counterpart: the reference's predict() is host code. */
+ * names the waiting role and site) since the last call that reported one: the
+ * word is cleared once it has been reported, so later launches are judged on
+ * their own.  No reference counterpart: the reference's predict() is host code. */
 hb_status hb_mlp_status(hb_mlp* handle, int32_t* device_status);
+
+/* Writes the handle's device status word from the host, as a kernel that gave up
+ * on a wait would.  Host-side fault injection for tests of the error path (no
+ * kernel is made to wait or fail).  No reference counterpart. */
+hb_status hb_mlp_inject_status(hb_mlp* handle, int32_t device_status);
 
 /* Profiling aid (bf16 kernel): SM cycle counters of the first cluster's leader CTA
  * for the most recent launch.  out[0..3] first epilogue group: waiting for its
@@ -254,11 +274,29 @@ hb_status hb_segment_sum(const float* values, const int64_t* offsets, int64_t n_
 /* Sum of each of n_planes contiguous planes of plane_len float32 values,
  * skipping NaN entries (pairs the reference would have raised on); used for
  * per-destination totals of hb_wave_out.scaled_ns.  out [n_planes] float64.
- * The partial sums of all calls share one scratch buffer of the library (allocated, and
- * grown, on the first call that needs it - a set-up step): calls on one device must be
- * ordered, on one stream or by events. */
+ * The partial sums of all calls on one GPU share a scratch buffer the library
+ * keeps for that GPU: calls on one GPU must be ordered, on one stream or by
+ * events.  The buffer is allocated by the first call on a GPU (room for 64
+ * planes) and replaced by a larger one when a call needs more; a replaced buffer
+ * is kept allocated until the process ends, so launches in flight and captured
+ * graphs that hold its address stay valid.  The allocating call is a set-up step:
+ * make it before a stream capture begins. */
 hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_t n_planes, double* out,
                        void* stream);
+
+/* Planes the plane-sum scratch of CUDA device `device` has room for (0 before the
+ * first call there, -1 for an ordinal out of range).  For tests of the per-GPU
+ * bookkeeping; no reference counterpart. */
+int64_t hb_plane_sum_scratch_planes(int32_t device);
+
+/* Sums of values grouped by a small key: out[g] = sum of values[i] with
+ * keys[i] == g, g < n_groups <= 256, float64, fixed order, NaN skipped.  With
+ * keys = the device row of each MLP query this gives the per-device totals of a
+ * batch of predictions (what summing Trace.run_time_ms per destination,
+ * analysis/trace.py:26-36, gives the reference).  Scratch and ordering as for
+ * hb_plane_sum (a buffer of its own, so the two may overlap). */
+hb_status hb_group_sum(const float* values, const uint8_t* keys, int64_t n, int32_t n_groups,
+                       double* out, void* stream);
 
 /* hb_plane_sum for callers that must not allocate device memory after start-up
  * (a process that gave the whole GPU to its own memory pool, or one that
@@ -275,6 +313,13 @@ hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_t n_planes,
  * It has no counterpart in the reference, whose totals are host-side sums. */
 hb_status hb_plane_sum_static(const float* values, int64_t plane_len, int32_t n_planes, double* out,
                               void* stream);
+
+/* Builds made with -DHB_BOUNDS_CHECK compare every table and element index of the
+ * wave-scaling kernels with its bound; the first violation is recorded in a device
+ * word (site << 24 | index, top bit set) and the access redirected, nothing traps.
+ * Synchronises, returns the word (0: none) and optionally clears it.  Ordinary
+ * builds return HB_ERR_UNSUPPORTED.  No reference counterpart. */
+hb_status hb_bounds_check_word(uint32_t* word, int32_t reset);
 
 #ifdef __cplusplus
 }

@@ -32,13 +32,17 @@ def run_wave_gpu(kernels, origin, dests, dest_regs=None, metrics=None):
     out = {k: to_numpy(getattr(res, k)) for k in
            ("scaled_ns", "dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves",
             "status", "limits")}
-    if metrics is None:
-        # the same call without the verification outputs takes the division-free kernel
-        fast = batched.wave_scale(kb, origin, dests, dest_regs=dr)
-        torch.cuda.synchronize()
-        out["fast_path"] = batched.wave_scale_path()
-        out["fast"] = {k: to_numpy(getattr(fast, k)) for k in
-                       ("scaled_ns", "dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves")}
+    # the same call without the block-limit planes takes the fastest kernel the rows allow:
+    # with the status plane ("fast") and without it ("plain")
+    names = ("scaled_ns", "dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves")
+    fast = batched.wave_scale(kb, origin, dests, dest_regs=dr, metrics=mb, want_status=True)
+    torch.cuda.synchronize()
+    out["fast_path"] = batched.wave_scale_path()
+    out["fast"] = {k: to_numpy(getattr(fast, k)) for k in names + ("status",)}
+    plain = batched.wave_scale(kb, origin, dests, dest_regs=dr, metrics=mb)
+    torch.cuda.synchronize()
+    out["plain_path"] = batched.wave_scale_path()
+    out["plain"] = {k: to_numpy(getattr(plain, k)) for k in names}
     return out
 
 
@@ -54,8 +58,10 @@ def assert_wave_equal(got, ref, rel=1e-6):
         assert np.array_equal(got[key], ref[key]), key
     ok = ref["status"] <= 1
     worst = 0.0
-    variants = [got] + ([got["fast"]] if "fast" in got else [])
+    variants = [got] + [got[name] for name in ("fast", "plain") if name in got]
     for v in variants:
+        if "status" in v:
+            assert np.array_equal(v["status"], ref["status"]), "status"
         for key in ("dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves"):
             assert np.array_equal(v[key], ref[key]), key
         assert np.isnan(v["scaled_ns"][~ok]).all()

@@ -73,7 +73,8 @@ def test_flatten_kernels_modes():
     with pytest.raises(AttributeError):
         wave_batch.flatten_kernels(ks, wave_batch.ROOFLINE)
     with pytest.raises(ZeroDivisionError):
-        wave_batch.raise_like_reference(np.array([[0, 2]]))
+        wave_batch.raise_like_reference(np.array([[1.5, np.nan]]))
+    wave_batch.raise_like_reference(np.array([[1.5, 2.5]]))
 
 
 def test_metadata_manager(tmp_path):
@@ -113,6 +114,20 @@ def test_run_times_and_operations():
     assert ns_to_ms(ms_to_ns(1.25)) == 1.25
     assert name_all_arguments(["a", "b"], (1,), {"b": 2, "c": 3}) == {"a": 1, "b": 2, "c": 3}
     assert {"conv2d", "gru"} <= SPECIAL_OPERATIONS
+
+
+def test_thread_block_occupancy_known_answers(device_file):
+    """KernelInstance.thread_block_occupancy is evaluated on the host by the library's own integer
+    code: the known answers of the reference's calculator, without a GPU."""
+    kat = [((256, 0, 0, 32), (8, 4, 8, 8)), ((1024, 0, 0, 65), (0, 0, 0, 0)),
+           ((128, 16384, 0, 40), (6, 4, 4, 6)), ((64, 0, 49152, 16), (2, 1, 1, 2)),
+           ((256, 8448, 0, 24), (8, 4, 7, 8)), ((96, 0, 40000, 72), (2, 1, 1, 2))]
+    for (block, dyn, static, regs), expect in kat:
+        k = KernelInstance("k", 100, block, dyn, static, regs, 1000)
+        got = tuple(k.thread_block_occupancy(device_file[n]) for n in ("V100", "T4", "P100", "P4000"))
+        assert got == expect
+    k = KernelInstance("k", 100, 256, 0, 0, 64, 1000)
+    assert k.thread_block_occupancy(device_file["V100"], 32) == 8
 
 
 def test_feature_extraction():

@@ -32,7 +32,7 @@ def _make(I, seed, origin_spec):
     return kernels, overhead, ops
 
 
-@pytest.mark.parametrize("I", [3, 64])
+@pytest.mark.parametrize("I", [3, 64, 512])
 def test_iteration_totals(bench_devices, I):
     origin, dests = bench_devices[0], bench_devices
     kernels, overhead, ops = _make(I, 4004, origin.spec_tuple())
@@ -49,14 +49,15 @@ def test_iteration_totals(bench_devices, I):
         off = torch.from_numpy(np.arange(I + 1, dtype=np.int64) * PER_ITER[op]).cuda()
         special[op] = iteration.SpecialOps(h, torch.from_numpy(feats).cuda(), torch.from_numpy(rt).cuda(), off)
 
-    totals, status = iteration.predict_iteration_totals(
+    totals, wave = iteration.predict_iteration_totals(
         batched.KernelBatch.from_numpy(kernels), torch.from_numpy(overhead).cuda(),
         torch.from_numpy(koff).cuda(), special, origin, dests, 0, list(range(6)))
     torch.cuda.synchronize()
     for s in special.values():
         s.handle.check_status()
     got = totals.cpu().numpy()
-    assert (status.cpu().numpy() <= 1).all()          # valid-only kernels never raise
+    assert not torch.isnan(wave.scaled_ns).any()       # valid-only kernels never raise
+    assert batched.wave_scale_path() == "wave_scale_lut_kernel"
 
     # reference: the oracle, float64, operation by operation
     specs = [d.spec_tuple() for d in dests]

@@ -162,3 +162,31 @@ def test_empty_and_single_query():
         ref = omlp.predict(w, feats[:1], dev[:1], DEVF, mu, sigma, np.float32)
         assert abs(float(one[0]) - ref[0]) <= 2e-2 * abs(ref[0])
         h.close()
+
+
+def test_timeout_status_is_reported_once():
+    """The error path of a bounded device-side wait, driven from the host: the status word a kernel
+    would leave is written by hand, the next status check reports HB_ERR_DEVICE_TIMEOUT with the
+    site, and the word is cleared so that later launches are judged on their own."""
+    from habitat_b200 import _native
+    w = workloads.torch_init_mlp_weights("bmm")
+    feats, dev = workloads.make_queries("bmm", 300, seed=5)
+    mu, sigma = workloads.batch_mu_sigma(feats, dev)
+    h = batched.MLPHandle(feats.shape[1], mu=mu, sigma=sigma,
+                          device_features=workloads.BENCH_DEVICE_FEATURES, **w)
+    d_f, d_r = torch.from_numpy(feats).cuda(), torch.from_numpy(dev).cuda()
+    first = h.predict(d_f, d_r).cpu().numpy()
+    h.check_status()
+    h.inject_status(0x212)                       # "MMA issuer gave up waiting for weights"
+    with pytest.raises(_native.HabitatNativeError) as err:
+        h.check_status()
+    assert err.value.status == _native.HB_ERR_DEVICE_TIMEOUT and "0x212" in str(err.value)
+    h.check_status()                             # reported once
+    h.inject_status(0x311)
+    with pytest.raises(_native.HabitatNativeError) as err:
+        h.predict_host(feats, dev)               # the host-buffer entry point checks the word itself
+    assert err.value.status == _native.HB_ERR_DEVICE_TIMEOUT
+    again = h.predict(d_f, d_r).cpu().numpy()
+    h.check_status()
+    assert np.array_equal(first, again)
+    h.close()

@@ -4,7 +4,6 @@ import pytest
 import torch
 
 from habitat_b200 import batched, workloads
-from habitat_b200.habitat_cuda import KernelInstance
 from oracle import wave as owave
 from tests.helpers import assert_wave_equal, run_wave_gpu, run_wave_oracle, to_numpy
 
@@ -75,6 +74,12 @@ def test_dest_regs(bench_devices):
     got = run_wave_gpu(kernels, bench_devices[0], bench_devices, dest_regs=dest_regs)
     ref = run_wave_oracle(kernels, bench_devices[0], bench_devices, dest_regs=dest_regs)
     assert_wave_equal(got, ref)
+    # register overrides and the status plane are served by the tabulated kernel
+    assert got["fast_path"] == "wave_scale_lut_kernel" and got["plain_path"] == "wave_scale_lut_kernel"
+    odd = {k: v[:K - 1] for k, v in kernels.items()}          # odd K: one record per thread
+    got = run_wave_gpu(odd, bench_devices[0], bench_devices, dest_regs=dest_regs[:, :K - 1])
+    assert got["fast_path"] == "wave_scale_lut_kernel"
+    assert_wave_equal(got, run_wave_oracle(odd, bench_devices[0], bench_devices, dest_regs=dest_regs[:, :K - 1]))
 
 
 def test_metrics_mode(device_file):
@@ -85,6 +90,9 @@ def test_metrics_mode(device_file):
     kernels = workloads.make_kernels(K, seed=21)
     metrics = workloads.make_metrics(K, seed=22)
     got = run_wave_gpu(kernels, origin, devs, metrics=metrics)
+    # gamma from raw metrics is computed inside the tabulated kernel (six rows with more than
+    # four shared-memory classes: every row's own tables)
+    assert got["fast_path"] == "wave_scale_lut_kernel" and got["plain_path"] == "wave_scale_lut_kernel"
     for d, dest in enumerate(devs):
         gam = np.array([
             owave.roofline_gamma(metrics["flop_efficiency_pct"][k], metrics["dram_read_bytes"][k],
@@ -95,8 +103,11 @@ def test_metrics_mode(device_file):
         k2 = dict(kernels, gamma=gam.astype(np.float32))
         ref = run_wave_oracle(k2, origin, [dest])
         one = {k: (v[d:d + 1] if k not in ("origin_occupancy", "origin_waves", "limits") else v)
-               for k, v in got.items()}
+               for k, v in got.items() if isinstance(v, np.ndarray)}
         one["limits"] = got["limits"][[0, d + 1]]
+        for name in ("fast", "plain"):
+            one[name] = {k: (v[d:d + 1] if k not in ("origin_occupancy", "origin_waves") else v)
+                         for k, v in got[name].items()}
         # gamma reaches the oracle rounded to float32; the device keeps float64
         assert_wave_equal(one, ref, rel=2e-6)
 
@@ -106,18 +117,6 @@ def test_host_buffer_entry_point(bench_devices):
     res = batched.wave_scale_host(kernels, bench_devices[0], bench_devices, want_status=True,
                                   want_limits=True)
     assert_wave_equal(res, run_wave_oracle(kernels, bench_devices[0], bench_devices))
-
-
-def test_thread_block_occupancy_known_answers(device_file):
-    kat = [((256, 0, 0, 32), (8, 4, 8, 8)), ((1024, 0, 0, 65), (0, 0, 0, 0)),
-           ((128, 16384, 0, 40), (6, 4, 4, 6)), ((64, 0, 49152, 16), (2, 1, 1, 2)),
-           ((256, 8448, 0, 24), (8, 4, 7, 8)), ((96, 0, 40000, 72), (2, 1, 1, 2))]
-    for (block, dyn, static, regs), expect in kat:
-        k = KernelInstance("k", 100, block, dyn, static, regs, 1000)
-        got = tuple(k.thread_block_occupancy(device_file[n]) for n in ("V100", "T4", "P100", "P4000"))
-        assert got == expect
-    k = KernelInstance("k", 100, 256, 0, 0, 64, 1000)
-    assert k.thread_block_occupancy(device_file["V100"], 32) == 8
 
 
 def test_reductions():
@@ -132,6 +131,14 @@ def test_reductions():
     planes[:, ::7] = np.nan
     got = batched.plane_sum(torch.from_numpy(planes).cuda()).cpu().numpy()
     assert np.allclose(got, np.nansum(planes.astype(np.float64), axis=1), rtol=1e-12)
+    # sums grouped by a key per element (per-device totals of MLP predictions), more than eight groups too
+    for n_groups in (1, 6, 8, 9, 20):
+        keys = g.integers(0, n_groups + 2, size=vals.size).astype(np.uint8)      # some keys beyond the groups
+        v = vals.copy()
+        v[::11] = np.nan
+        got = batched.group_sum(torch.from_numpy(v).cuda(), torch.from_numpy(keys).cuda(), n_groups).cpu().numpy()
+        ref = np.array([np.nansum(v[keys == k].astype(np.float64)) for k in range(n_groups)])
+        assert np.allclose(got, ref, rtol=1e-12, atol=1e-9), n_groups
     rt = g.uniform(0.02, 50, 1000).astype(np.float32)
     pd = g.normal(1, 1, 1000).astype(np.float32)
     po = g.uniform(0.5, 2, 1000).astype(np.float32)
@@ -212,3 +219,78 @@ def test_many_destinations(device_file, D):
     got = run_wave_gpu(kernels, device_file["V100"], dests)
     assert got["fast_path"] == "wave_scale_kernel"
     assert_wave_equal(got, run_wave_oracle(kernels, device_file["V100"], dests))
+
+
+def test_plane_sum_scratch_is_kept_per_gpu():
+    """The partial sums live in a buffer per GPU that only ever grows and is never freed while a
+    launch (or a captured graph) may hold it."""
+    from habitat_b200 import _native
+    lib = _native.load()
+    dev = torch.cuda.current_device()
+    g = workloads.rng(43)
+    small = torch.from_numpy(g.uniform(0, 10, size=(3, 4096)).astype(np.float32)).cuda()
+    out_small = batched.plane_sum(small)
+    have = lib.hb_plane_sum_scratch_planes(dev)
+    assert have >= 64
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        out_graph = torch.empty(3, dtype=torch.float64, device="cuda")
+        batched.plane_sum(small, out=out_graph)          # warm-up outside the capture
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            batched.plane_sum(small, out=out_graph)
+    big = torch.from_numpy(g.uniform(0, 10, size=(4 * have + 1, 512)).astype(np.float32)).cuda()
+    out_big = batched.plane_sum(big)                     # needs a larger buffer
+    assert lib.hb_plane_sum_scratch_planes(dev) >= 4 * have + 1
+    out_graph.zero_()
+    graph.replay()                                       # still refers to the first buffer
+    torch.cuda.synchronize()
+    assert torch.equal(out_graph, out_small)
+    assert np.allclose(out_big.cpu().numpy(), big.double().sum(dim=1).cpu().numpy(), rtol=1e-12)
+    assert lib.hb_plane_sum_scratch_planes(-1) == -1 and lib.hb_plane_sum_scratch_planes(63) == 0
+
+
+def test_index_checked_build(bench_devices):
+    """The same library built with -DHB_BOUNDS_CHECK (every table and element index of the
+    wave-scaling kernels compared with its bound, violations recorded, nothing traps): results equal
+    the oracle's and no index is ever out of range, on the edge records and on a plain batch."""
+    import os
+    import subprocess
+    import sys
+    from habitat_b200 import build as hb_build
+    if not os.path.exists(hb_build.CHECKED_LIB_PATH):
+        pytest.fail("libhabitat_b200_checked.so is not built (python -m habitat_b200.build --checked)")
+    code = """
+import ctypes, sys
+import numpy as np
+sys.path.insert(0, %r)
+from habitat_b200 import _native, device_table, workloads
+from tests.helpers import assert_wave_equal, run_wave_gpu, run_wave_oracle
+from tests.test_wave_scale_gpu import _edge_records
+devs = device_table.load_device_file()
+bench = [devs[n] for n in workloads.BENCH_DEVICES]
+lib = _native.load()
+word = ctypes.c_uint32(7)
+assert lib.hb_bounds_check_word(ctypes.byref(word), 1) == 0 and word.value == 0
+g = workloads.rng(5)
+for kernels in (_edge_records(bench), workloads.make_kernels(20001, seed=3)):
+    K = len(kernels["num_blocks"])
+    regs = g.integers(-1, 300, size=(6, K)).astype(np.int16)
+    for dr in (None, regs):
+        got = run_wave_gpu(kernels, bench[0], bench, dest_regs=dr)
+        assert got["fast_path"] == "wave_scale_lut_kernel"
+        assert_wave_equal(got, run_wave_oracle(kernels, bench[0], bench, dest_regs=dr))
+    got = run_wave_gpu(kernels, bench[0], bench, metrics=workloads.make_metrics(K, seed=4))
+    assert got["fast_path"] == "wave_scale_lut_kernel"
+assert lib.hb_bounds_check_word(ctypes.byref(word), 0) == 0
+assert word.value == 0, hex(word.value)
+print("checked build ok")
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, HABITAT_B200_LIB=hb_build.CHECKED_LIB_PATH)
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "checked build ok" in r.stdout, r.stdout + r.stderr
+    # the ordinary build says that it carries no checks
+    from habitat_b200 import _native
+    import ctypes
+    assert _native.load().hb_bounds_check_word(ctypes.byref(ctypes.c_uint32(0)), 0) == _native.HB_ERR_UNSUPPORTED
