@@ -457,7 +457,43 @@ __device__ __forceinline__ uint32_t hb_checked(uint32_t idx, uint32_t limit, uin
 #define HB_IDX(idx, limit, site) (idx)
 #endif
 
-template <int VEC, bool EXT, int NP, int NS>
+// Two records per thread (VEC = 2) need the inputs on 8-byte boundaries; ALIGNED says that the
+// output planes are too (K even), so results leave as 8-byte stores.  Otherwise (odd K: every
+// other plane starts on an odd element) the same two-record arithmetic ends in scalar stores,
+// and the thread that owns the last, single record loads it alone.
+template <typename T, int VEC, bool ALIGNED>
+__device__ __forceinline__ Vec<T, VEC> load_pair(const T* q, bool pair) {
+  if (VEC == 1 || ALIGNED) return load_vec<T, VEC>(q);
+  Vec<T, VEC> v;
+  if (pair) {
+    v = load_vec<T, VEC>(q);
+  } else {
+    v.v[0] = q[0];
+    v.v[VEC - 1] = q[0];
+  }
+  return v;
+}
+template <typename T, int VEC, bool ALIGNED>
+__device__ __forceinline__ void store_pair(T* q, const Vec<T, VEC>& v, bool pair) {
+  if (VEC == 1 || ALIGNED) {
+    store_vec<T, VEC>(q, v);
+  } else {
+    q[0] = v.v[0];
+    if (pair) q[VEC - 1] = v.v[VEC - 1];
+  }
+}
+// The low bytes of the two 16-bit halves of `pair_word` as one or two bytes at q.
+template <int VEC, bool ALIGNED>
+__device__ __forceinline__ void store_byte_pair(uint8_t* q, uint32_t pair_word, bool pair) {
+  if (VEC == 2 && ALIGNED) {
+    *reinterpret_cast<uint16_t*>(q) = static_cast<uint16_t>(__byte_perm(pair_word, 0u, 0x4420u));
+  } else {
+    q[0] = static_cast<uint8_t>(pair_word);
+    if (VEC == 2 && pair) q[1] = static_cast<uint8_t>(pair_word >> 16);
+  }
+}
+
+template <int VEC, bool EXT, bool ALIGNED, int NP, int NS>
 __global__ void __launch_bounds__(kLutThreads, EXT ? 8 : 12)
 wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
   hb_grid_dependency_wait();
@@ -470,13 +506,14 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
   const bool with_status = EXT && p.status != nullptr;
 
   for (uint32_t k0 = (blockIdx.x * kLutThreads + threadIdx.x) * VEC; k0 < K; k0 += stride) {
-    const Vec<int32_t, VEC> nbv = load_vec<int32_t, VEC>(p.num_blocks + k0);
-    const Vec<uint16_t, VEC> bsv = load_vec<uint16_t, VEC>(p.block_size + k0);
-    const Vec<uint16_t, VEC> rgv = load_vec<uint16_t, VEC>(p.regs + k0);
-    const Vec<uint32_t, VEC> smv = load_vec<uint32_t, VEC>(p.smem + k0);
-    const Vec<float, VEC> tv = load_vec<float, VEC>(p.time_ns + k0);
+    const bool pair = VEC == 2 && (ALIGNED || k0 + 1 < K);   // false: the last record of an odd batch
+    const Vec<int32_t, VEC> nbv = load_pair<int32_t, VEC, ALIGNED>(p.num_blocks + k0, pair);
+    const Vec<uint16_t, VEC> bsv = load_pair<uint16_t, VEC, ALIGNED>(p.block_size + k0, pair);
+    const Vec<uint16_t, VEC> rgv = load_pair<uint16_t, VEC, ALIGNED>(p.regs + k0, pair);
+    const Vec<uint32_t, VEC> smv = load_pair<uint32_t, VEC, ALIGNED>(p.smem + k0, pair);
+    const Vec<float, VEC> tv = load_pair<float, VEC, ALIGNED>(p.time_ns + k0, pair);
     Vec<float, VEC> gv;
-    if (!with_metrics) gv = load_vec<float, VEC>(p.gamma + k0);
+    if (!with_metrics) gv = load_pair<float, VEC, ALIGNED>(p.gamma + k0, pair);
 
     uint32_t P[2] = {0u, 0u}, S[2] = {0u, 0u};   // class bytes of the two records
     uint32_t wrow[2] = {0u, 0u};                 // EXT: warps per block x row length (P index base)
@@ -504,9 +541,10 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
       if (with_metrics) {
         // wave_scaling/roofline.py:68-92, float64, same operation order
         double x = -1.0;   // "no metrics" or next to no floating-point work: gamma = 1
-        if (p.has_metrics[k0 + i]) {
-          const double total_gb = (p.dram_read[k0 + i] + p.dram_write[k0 + i]) / 1024 / 1024 / 1024;
-          const double gps = p.flop_eff[k0 + i] / 100 * lp.origin_peak;
+        const uint32_t ki = (i == 0 || pair) ? k0 + i : k0;   // the tail thread's second slot repeats the first
+        if (p.has_metrics[ki]) {
+          const double total_gb = (p.dram_read[ki] + p.dram_write[ki]) / 1024 / 1024 / 1024;
+          const double gps = p.flop_eff[ki] / 100 * lp.origin_peak;
           const double gf = gps * static_cast<double>(tv.v[i]) / 1e9;
           if (gf < 1e-9) x = -1.0;
           else if (total_gb == 0) x = -2.0;   // gamma = 0
@@ -548,12 +586,8 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
       const uint32_t om = fits_o[i] ? __umulhi(static_cast<uint32_t>(nb) + og.sm.x, og.sm.y) : 1u;
       lg_o[i] = __ldg(reinterpret_cast<const float2*>(tab_t + (og.sel.z + HB_IDX(om, kLutOcc, 4) * 16u + 8u)));
     }
-    if (VEC == 2) {
-      *reinterpret_cast<uint16_t*>(p.origin_occ + k0) = static_cast<uint16_t>(__byte_perm(o2, 0u, 0x4420u));
-    } else {
-      p.origin_occ[k0] = static_cast<uint8_t>(o2);
-    }
-    store_vec<uint32_t, VEC>(p.origin_waves + k0, owav);
+    store_byte_pair<VEC, ALIGNED>(p.origin_occ + k0, o2, pair);
+    store_pair<uint32_t, VEC, ALIGNED>(p.origin_waves + k0, owav, pair);
 
 #pragma unroll 1
     for (int d = 0; d < D; ++d) {
@@ -564,7 +598,14 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
         occ2 = __vimin_s16x2_relu(prmt(P[0], P[1], dd.sel.x), prmt(S[0], S[1], dd.sel.y));
       } else {
         Vec<int16_t, VEC> drv;
-        if (with_regs) drv = load_vec<int16_t, VEC>(p.dest_regs + base);
+        if (with_regs) {
+          if (VEC == 1 || ALIGNED) {
+            drv = load_vec<int16_t, VEC>(p.dest_regs + base);
+          } else {
+            drv.v[0] = p.dest_regs[base];
+            drv.v[VEC - 1] = pair ? p.dest_regs[base + 1] : static_cast<int16_t>(-1);
+          }
+        }
         occ2 = 0;
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
@@ -615,18 +656,13 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
         if (with_status) {
           const uint32_t st = !nbok[i] ? HB_PAIR_BAD_INPUT
                                        : (!ok ? HB_PAIR_ZERO_WAVE : (small ? HB_PAIR_SMALL : HB_PAIR_LARGE));
-          st2 |= st << (8 * i);
+          st2 |= st << (16 * i);
         }
       }
-      store_vec<float, VEC>(p.scaled_ns + base, outv);
-      store_vec<uint32_t, VEC>(p.dest_waves + base, wavv);
-      if (VEC == 2) {
-        *reinterpret_cast<uint16_t*>(p.dest_occ + base) = static_cast<uint16_t>(__byte_perm(occ2, 0u, 0x4420u));
-        if (with_status) *reinterpret_cast<uint16_t*>(p.status + base) = static_cast<uint16_t>(st2);
-      } else {
-        p.dest_occ[base] = static_cast<uint8_t>(occ2);
-        if (with_status) p.status[base] = static_cast<uint8_t>(st2);
-      }
+      store_pair<float, VEC, ALIGNED>(p.scaled_ns + base, outv, pair);
+      store_pair<uint32_t, VEC, ALIGNED>(p.dest_waves + base, wavv, pair);
+      store_byte_pair<VEC, ALIGNED>(p.dest_occ + base, occ2, pair);
+      if (with_status) store_byte_pair<VEC, ALIGNED>(p.status + base, st2, pair);
     }
   }
 }
@@ -780,18 +816,19 @@ int class_of(int* rows, int* n, int row, Same same) {
   return (*n)++;
 }
 
-template <int VEC, bool EXT, int NP, int NS>
+template <int VEC, bool EXT, bool ALIGNED, int NP, int NS>
 cudaError_t launch_lut(unsigned grid, cudaStream_t stream, const Ptrs& p, const LutParams& q) {
-  return hb::launch_overlapped(wave_scale_lut_kernel<VEC, EXT, NP, NS>, dim3(grid), dim3(kLutThreads), 0, stream, p, q);
+  return hb::launch_overlapped(wave_scale_lut_kernel<VEC, EXT, ALIGNED, NP, NS>, dim3(grid), dim3(kLutThreads), 0,
+                               stream, p, q);
 }
 
 template <int NP>
 cudaError_t launch_lut_plain(int ns, unsigned grid, cudaStream_t stream, const Ptrs& p, const LutParams& q) {
   switch (ns) {
-    case 1: return launch_lut<2, false, NP, 1>(grid, stream, p, q);
-    case 2: return launch_lut<2, false, NP, 2>(grid, stream, p, q);
-    case 3: return launch_lut<2, false, NP, 3>(grid, stream, p, q);
-    default: return launch_lut<2, false, NP, 4>(grid, stream, p, q);
+    case 1: return launch_lut<2, false, true, NP, 1>(grid, stream, p, q);
+    case 2: return launch_lut<2, false, true, NP, 2>(grid, stream, p, q);
+    case 3: return launch_lut<2, false, true, NP, 3>(grid, stream, p, q);
+    default: return launch_lut<2, false, true, NP, 4>(grid, stream, p, q);
   }
 }
 
@@ -845,21 +882,30 @@ bool try_launch_lut(const Ptrs& p, const LaunchParams& lp, int sm_count, cudaStr
   auto al = [](const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; };
   const bool metrics = p.has_metrics != nullptr;
   const bool ext = metrics || p.dest_regs != nullptr || p.status != nullptr || many_classes;
-  const bool vec2 = K % 2 == 0 && al(p.num_blocks, 8) && al(p.smem, 8) && al(p.time_ns, 8) &&
-                    (metrics || al(p.gamma, 8)) && al(p.block_size, 4) && al(p.regs, 4) && al(p.scaled_ns, 8) &&
-                    al(p.dest_waves, 8) && al(p.origin_waves, 8) && al(p.dest_occ, 2) && al(p.origin_occ, 2) &&
-                    (!p.status || al(p.status, 2)) && (!p.dest_regs || al(p.dest_regs, 4));
+  // two records per thread when the inputs sit on 8-byte boundaries; 8-byte stores when the
+  // output planes do too (K even)
+  const bool vec2 = al(p.num_blocks, 8) && al(p.smem, 8) && al(p.time_ns, 8) && (metrics || al(p.gamma, 8)) &&
+                    al(p.block_size, 4) && al(p.regs, 4) && K >= 2;
+  const bool aligned = vec2 && K % 2 == 0 && al(p.scaled_ns, 8) && al(p.dest_waves, 8) && al(p.origin_waves, 8) &&
+                       al(p.dest_occ, 2) && al(p.origin_occ, 2) && (!p.status || al(p.status, 2)) &&
+                       (!p.dest_regs || al(p.dest_regs, 4));
   const int vec = vec2 ? 2 : 1;
   const int64_t blocks = ((K + vec - 1) / vec + kLutThreads - 1) / kLutThreads;
-  // persistent grid: at most HB_LUT_BLOCKS_PER_SM resident blocks per SM stride over the batch
-  static const int per_sm = [] { const char* e = std::getenv("HB_LUT_BLOCKS_PER_SM"); return e ? std::atoi(e) : 12; }();
-  const int64_t cap = per_sm > 0 ? static_cast<int64_t>(sm_count) * (ext ? (per_sm < 8 ? per_sm : 8) : per_sm) : blocks;
+  // One block per 128 threads' worth of records measured fastest at every batch size (the block
+  // scheduler balances the tail); HB_LUT_BLOCKS_PER_SM = n caps the grid at n blocks per SM, which
+  // then stride over the batch.
+  static const int per_sm = [] { const char* e = std::getenv("HB_LUT_BLOCKS_PER_SM"); return e ? std::atoi(e) : 0; }();
+  const int64_t cap = per_sm > 0 ? static_cast<int64_t>(sm_count) * per_sm : blocks;
   const unsigned grid = static_cast<unsigned>(blocks < cap ? blocks : cap);
   cudaError_t le;
   if (ext) {
-    le = vec2 ? launch_lut<2, true, 1, 1>(grid, stream, p, q) : launch_lut<1, true, 1, 1>(grid, stream, p, q);
+    le = !vec2 ? launch_lut<1, true, true, 1, 1>(grid, stream, p, q)
+               : (aligned ? launch_lut<2, true, true, 1, 1>(grid, stream, p, q)
+                          : launch_lut<2, true, false, 1, 1>(grid, stream, p, q));
   } else if (!vec2) {
-    le = launch_lut<1, false, 4, 4>(grid, stream, p, q);
+    le = launch_lut<1, false, true, 4, 4>(grid, stream, p, q);
+  } else if (!aligned) {
+    le = launch_lut<2, false, false, 4, 4>(grid, stream, p, q);
   } else {
     switch (n_p) {
       case 1: le = launch_lut_plain<1>(n_s, grid, stream, p, q); break;

@@ -32,6 +32,25 @@ def init(backend=None):
     return rank, world
 
 
+_host_group = None
+
+
+def host_group():
+    """A gloo group over the same ranks, for waits that should not occupy the GPUs: a rank
+    blocked in a NCCL barrier spins on its GPU, a rank blocked here sleeps on a socket."""
+    global _host_group
+    if _host_group is None and dist.is_initialized() and dist.get_world_size() > 1:
+        _host_group = dist.new_group(backend="gloo")
+    return _host_group
+
+
+def host_barrier():
+    """Barrier over the host group (no-op on one rank).  All ranks must call it."""
+    g = host_group()
+    if g is not None:
+        dist.barrier(group=g)
+
+
 def shard_bounds(n, rank, world):
     """Contiguous near-equal shards: the first n % world ranks hold one more item."""
     base, extra = divmod(n, world)

@@ -149,3 +149,75 @@ def torch_init_mlp_weights(op, seed=None, layers=8, width=1024):
     finally:
         torch.random.set_rng_state(state)
     return state_to_arrays(pred.model)
+
+
+# ---------------------------------------------------------------------------
+# The fixed batch of the scale sweep: 67,108,864 (kernel, destination) pairs = 11,184,811 kernels
+# x 6 destinations (the last kernel rounds the pair count up by two) and 4,194,304 queries for
+# each of the four predictors.  Records are generated in chunks of 262,144 from per-chunk seeds,
+# so any rank can produce exactly its shard [lo, hi) without generating the rest.
+# ---------------------------------------------------------------------------
+SWEEP_KERNELS = 11_184_811
+SWEEP_QUERIES = 4_194_304
+SWEEP_OPS = ("conv2d", "linear", "bmm", "lstm")
+SWEEP_CHUNK = 1 << 18
+
+
+def _chunked(lo, hi, make):
+    """Concatenates make(chunk index) over the chunks that overlap [lo, hi) and cuts to it."""
+    parts = []
+    for c in range(lo // SWEEP_CHUNK, (max(hi, lo + 1) - 1) // SWEEP_CHUNK + 1):
+        part = make(c)
+        a = max(lo - c * SWEEP_CHUNK, 0)
+        b = min(hi - c * SWEEP_CHUNK, SWEEP_CHUNK)
+        parts.append(tuple(x[a:b] for x in part))
+    return [np.concatenate([p[i] for p in parts]) for i in range(len(parts[0]))]
+
+
+def sweep_kernels(lo, hi, seed=5000):
+    """Records [lo, hi) of the sweep's kernel batch (same fields as make_kernels)."""
+    names = ("num_blocks", "block_size", "regs_per_thread", "smem_bytes", "run_time_ns", "gamma")
+    cols = _chunked(lo, hi, lambda c: tuple(make_kernels(SWEEP_CHUNK, seed + c)[n] for n in names))
+    return dict(zip(names, cols))
+
+
+def sweep_queries(op, lo, hi, seed=6000):
+    """Queries [lo, hi) of the sweep's batch for predictor `op`: ([n, F] float32, [n] uint8)."""
+    base = seed + 1000 * SWEEP_OPS.index(op)
+    feats, dev = _chunked(lo, hi, lambda c: make_queries(op, SWEEP_CHUNK, base + c))
+    return feats, dev
+
+
+def sweep_mu_sigma(op, seed=6000):
+    """Normalisation of the sweep's predictor `op`: mean / population std over the first chunk
+    of its batch (every rank computes the same values without seeing the whole batch)."""
+    feats, dev = sweep_queries(op, 0, SWEEP_CHUNK, seed)
+    return batch_mu_sigma(feats, dev)
+
+
+# ---------------------------------------------------------------------------
+# The mixed iteration trace: every iteration holds 53 conv2d, 1 linear and 32 bmm operations
+# predicted by their MLPs and 74 ordinary operations of one wave-scaled kernel each.
+# ---------------------------------------------------------------------------
+ITER_SPECIAL = {"conv2d": 53, "linear": 1, "bmm": 32}
+ITER_KERNELS = 74
+
+
+def make_iterations(lo, hi, origin_occupancy, seed=4000):
+    """Iterations [lo, hi) of the mixed trace, generated per iteration from its own seed.
+    origin_occupancy(block, smem, regs) -> occupancy array on the origin (kernels are
+    rejection-sampled so that the origin can run them).  Returns (kernels dict, overhead_ns
+    float32 [n * 74], {op: (features, measured ms)})."""
+    ks, over, ops = [], [], {op: ([], []) for op in ITER_SPECIAL}
+    for it in range(lo, hi):
+        ks.append(make_kernels(ITER_KERNELS, seed + 10 * it, valid_only=True, origin=origin_occupancy))
+        g = rng(seed + 10 * it + 1)
+        over.append(g.uniform(0, 10_000, size=ITER_KERNELS).astype(np.float32))
+        for j, (op, n) in enumerate(ITER_SPECIAL.items()):
+            feats, _ = make_queries(op, n, seed + 10 * it + 2 + j)
+            ops[op][0].append(feats)
+            ops[op][1].append(np.exp(g.uniform(np.log(0.02), np.log(50.0), size=n)).astype(np.float32))
+    kernels = {k: np.concatenate([x[k] for x in ks]) for k in ks[0]} if ks else make_kernels(0, seed)
+    special = {op: (np.concatenate(f) if f else np.zeros((0, len(OP_FEATURES[op])), np.float32),
+                    np.concatenate(t) if t else np.zeros(0, np.float32)) for op, (f, t) in ops.items()}
+    return kernels, (np.concatenate(over) if over else np.zeros(0, np.float32)), special

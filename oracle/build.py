@@ -22,7 +22,9 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 BUILD_DIR = os.path.join(HERE, "_build")
 REF_DIR = os.path.join(HERE, "_ref")
-REFERENCE_ROOT = os.environ.get("HABITAT_REFERENCE_ROOT", "/root/reference")
+# the reference tree: HABITAT_REFERENCE_ROOT, else a `reference` directory beside this repository
+REFERENCE_ROOT = os.environ.get("HABITAT_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(HERE)), "reference")
 CUDA_INCLUDE = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
 
 

@@ -1,6 +1,7 @@
 """Generates the golden fixtures in this directory from the reference itself.
 
-Run where the reference tree is mounted (default /root/reference):
+Run where the reference tree is mounted (HABITAT_REFERENCE_ROOT, default: a `reference`
+directory beside this repository):
 
     python tests/golden/make_golden.py
 
@@ -37,7 +38,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("HABITAT_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("HABITAT_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
 os.environ["TORCH_FORCE_NO_WEIGHTS_ONLY_LOAD"] = "1"   # the checkpoints hold numpy arrays
 
 import torch  # noqa: E402

@@ -1,4 +1,4 @@
-"""Host pipelines (pinned memory in and out, two streams) against the device entry points."""
+"""Host pipelines (one pinned block in, pinned results out, three streams) against the device entry points."""
 import numpy as np
 import pytest
 import torch
@@ -9,28 +9,19 @@ from tests.helpers import run_wave_oracle, to_numpy
 pytestmark = pytest.mark.gpu
 
 
-def _pinned(arrays):
-    out = {}
-    for k, v in arrays.items():
-        a = np.ascontiguousarray(v.astype(np.float32) if k == "run_time_ns" else v)
-        if a.dtype == np.uint16:
-            a = a.view(np.int16)
-        elif a.dtype == np.uint32:
-            a = a.view(np.int32)
-        out[k] = torch.from_numpy(a).pin_memory()
-    return out
-
-
 def test_wave_scale_pipeline(bench_devices):
     K = 40000
     batches = [workloads.make_kernels(K, seed=300 + i) for i in range(5)]
-    pipe = hostio.WaveScaleHost(bench_devices[0], bench_devices, K, depth=2)
+    every = ("scaled_ns", "dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves")
+    pipe = hostio.WaveScaleHost(bench_devices[0], bench_devices, K, depth=3, results=every)
+    blocks = [hostio.pack_kernels(b) for b in batches]
+    assert blocks[0].is_pinned() and blocks[0].numel() == 20 * K
     for i, b in enumerate(batches):
-        slot = i % 2
-        pipe.wait(slot)                      # results of batch i - 2 were consumed below
-        pipe.submit(_pinned(b), slot)
+        slot = i % 3
+        pipe.wait(slot)                      # results of batch i - 3 were consumed below
+        pipe.submit(blocks[i], slot)
         if i >= 1:                           # check the previous batch while this one runs
-            prev = (i - 1) % 2
+            prev = (i - 1) % 3
             pipe.wait(prev)
             ref = run_wave_oracle(batches[i - 1], bench_devices[0], bench_devices)
             got = {k: to_numpy(v) for k, v in pipe.host_out[prev].items()}
@@ -44,7 +35,7 @@ def test_wave_scale_pipeline(bench_devices):
 
     # only the predicted times copied back; the other outputs stay on the device
     times = hostio.WaveScaleHost(bench_devices[0], bench_devices, K, depth=2, results=("scaled_ns",))
-    times.submit(_pinned(batches[0]), 0)
+    times.submit(blocks[0], 0)
     times.wait(0)
     ref = run_wave_oracle(batches[0], bench_devices[0], bench_devices)
     ok = ref["status"] <= 1
@@ -54,6 +45,15 @@ def test_wave_scale_pipeline(bench_devices):
     assert np.array_equal(to_numpy(times.dev_out[0].dest_occupancy), ref["dest_occupancy"])
     with pytest.raises(ValueError):
         hostio.WaveScaleHost(bench_devices[0], bench_devices, K, results=("scaled",))
+    with pytest.raises(ValueError):
+        times.submit(blocks[0][:-20], 1)
+    # pinned pages are placed near the GPU when the topology can be read; either way the
+    # thread's CPU set is what it was afterwards
+    import os
+    before = os.sched_getaffinity(0)
+    with hostio.numa_local(torch.cuda.current_device()) as cpus:
+        assert cpus is None or cpus <= before
+    assert os.sched_getaffinity(0) == before
 
 
 def test_mlp_pipeline():
@@ -63,13 +63,13 @@ def test_mlp_pipeline():
     mu, sigma = workloads.batch_mu_sigma(feats, dev)
     h = batched.MLPHandle(4, mu=mu, sigma=sigma, device_features=workloads.BENCH_DEVICE_FEATURES, **w)
     want = h.predict(torch.from_numpy(feats).cuda(), torch.from_numpy(dev).cuda()).cpu()
-    pipe = hostio.MLPPredictHost(h, Q, depth=2)
+    pipe = hostio.MLPPredictHost(4, Q + 100, depth=2)          # buffers may be larger than a batch
     pf, pr = torch.from_numpy(feats).pin_memory(), torch.from_numpy(dev).pin_memory()
     for i in range(4):
         pipe.wait(i % 2)
-        pipe.submit(pf, pr, i % 2)
+        pipe.submit(h, pf, pr, i % 2)
     for slot in range(2):
         pipe.wait(slot)
-        assert torch.equal(pipe.host_out[slot], want)
+        assert torch.equal(pipe.host_out[slot][:Q], want)
     h.check_status()
     h.close()
