@@ -1,8 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the batched prediction path on the fixed batch of the scale sweep.
 
-One JSON line on stdout (rank 0).  A step is one pass over the whole batch: 67,108,866
-(kernel x destination) pairs of wave scaling (11,184,811 kernels to six device rows) plus
+One JSON line on stdout (rank 0).  A step is one pass over the whole batch: 67,108,872
+(kernel x destination) pairs of wave scaling (11,184,812 kernels to six device rows) plus
 16,777,216 MLP queries (4,194,304 for each of the conv2d, linear, bmm and lstm predictors).
 Under torchrun (one rank per GPU) the batch is sharded: every rank takes a contiguous range of
 kernels and of each predictor's queries, and each step ends its two phases with one NCCL
@@ -125,7 +125,7 @@ def dist_env():
         int(os.environ.get("WORLD_SIZE", 1))
 
 
-SWEEP_WORKLOAD = ("config 5: scale sweep, a fixed batch of 67,108,866 wave-scaling pairs (11,184,811 synthetic "
+SWEEP_WORKLOAD = ("config 5: scale sweep, a fixed batch of 67,108,872 wave-scaling pairs (11,184,812 synthetic "
                   "kernels from a V100-class origin to 6 device rows) plus 16,777,216 MLP queries (4,194,304 each "
                   "for the conv2d, linear, bmm and lstm predictors), sharded over the GPUs")
 
@@ -251,6 +251,24 @@ class Ctx:
                 sys.stdout.flush()
                 os.dup2(saved, 1)
                 os.close(saved)
+        # Totals across ranks: by default exchanged inside the reduction kernels through peer
+        # memory (habitat_b200/csrc/peer_exchange.cu), with NCCL all-reduces as the other choice,
+        # as the cross-check in the warm-up steps and as the fallback if the set-up fails anywhere.
+        self.peer = None
+        self.totals_via = "nccl" if self.world > 1 else "none"
+        if self.world > 1 and args.totals == "peer":
+            ok = 1.0
+            try:
+                self.peer = hd.PeerTotals()
+            except Exception as exc:                       # noqa: BLE001 - any failure means NCCL
+                print("peer exchange unavailable on rank %d: %s" % (self.rank, exc), file=sys.stderr)
+                ok = 0.0
+            flag = torch.tensor([ok], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if float(flag.item()) == 1.0:
+                self.totals_via = "peer"
+            else:
+                self.peer = None
         self.peaks = load_peaks()
         devs = device_table.load_device_file()
         self.bench_devs = [devs[n] for n in workloads.BENCH_DEVICES]
@@ -550,11 +568,14 @@ class Sweep:
         self.flush = torch.empty((L2_FLUSH_BYTES,), dtype=torch.uint8, device="cuda")
         self.ev = []
 
-    def step(self, i, timed=True):
+    def step(self, i, timed=True, via=None):
         """One pass over the shard: wave-scaling phase, then the MLP phase; each ends with the
-        all-reduce of its totals.  Events bracket the phases and the dominant kernels."""
+        all-reduce of its totals (via "peer": inside the final stage of the reductions, through
+        peer memory; via "nccl": one NCCL all-reduce per phase).  Events bracket the phases and
+        the dominant kernels."""
         ctx, torch = self.ctx, self.ctx.torch
         from habitat_b200 import batched
+        via = via or ctx.totals_via
         s = ctx.stream
         tot = self.totals[i]
         ev = {k: ctx.event() for k in ("w0", "k1", "w1", "m0", "m1")} if timed else None
@@ -564,9 +585,12 @@ class Sweep:
         batched.wave_scale(self.kb, ctx.origin, ctx.bench_devs, out=self.out)
         if timed:
             ev["k1"].record(s)
-        batched.plane_sum(self.out.scaled_ns, out=tot[:WAVE_D])
-        if ctx.world > 1:
-            ctx.dist.all_reduce(tot[:WAVE_D])
+        if via == "peer":
+            ctx.peer.plane_sum(self.out.scaled_ns, out=tot[:WAVE_D])
+        else:
+            batched.plane_sum(self.out.scaled_ns, out=tot[:WAVE_D])
+            if via == "nccl":
+                ctx.dist.all_reduce(tot[:WAVE_D])
         if timed:
             ev["w1"].record(s)
             ev["m0"].record(s)
@@ -580,9 +604,12 @@ class Sweep:
             if timed:
                 b.record(s)
                 pk.append((a, b))
-            batched.group_sum(self.d_o[op], self.d_r[op], WAVE_D,
-                              out=tot[WAVE_D * (1 + j):WAVE_D * (2 + j)])
-        if ctx.world > 1:
+            part = tot[WAVE_D * (1 + j):WAVE_D * (2 + j)]
+            if via == "peer":
+                ctx.peer.group_sum(self.d_o[op], self.d_r[op], WAVE_D, out=part)
+            else:
+                batched.group_sum(self.d_o[op], self.d_r[op], WAVE_D, out=part)
+        if via == "nccl":
             ctx.dist.all_reduce(tot[WAVE_D:])
         if timed:
             ev["m1"].record(s)
@@ -889,6 +916,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg and the oracle checks")
+    ap.add_argument("--totals", default="peer", choices=["peer", "nccl"],
+                    help="how the per-step totals are summed across GPUs")
     ap.add_argument("--case", default="all",
                     choices=["all", "config2", "config2-large", "config2-status", "config2-regs", "config2-metrics",
                              "config3", "config1"],
@@ -923,10 +952,29 @@ def main():
 
     with torch.cuda.stream(ctx.stream):
         sw = Sweep(ctx, steps + warm)
+        ctx.barrier()                 # ranks meet on the host before the first exchange between GPUs
+        exchange_check = None
         for i in range(warm):
-            sw.step(i, timed=False)
+            # the first warm-up step always takes NCCL: its totals check the peer exchange of the others
+            sw.step(i, timed=False, via="nccl" if (i == 0 and world > 1) else None)
         for h in sw.handles.values():
             h.check_status()          # a launch that gave up on a device-side wait ends the run here
+        if ctx.totals_via == "peer":
+            bad = 0.0
+            try:
+                ctx.peer.check_status()
+                t = sw.totals[:warm].cpu().numpy()
+                rel = np.abs(t[1:] - t[0]) / np.abs(t[0])
+                exchange_check = float(rel.max())
+                if not (rel.max() <= 1e-12):
+                    bad = 1.0
+            except Exception as exc:                       # noqa: BLE001 - a wait that ran out, or NaN totals
+                print("peer exchange failed its warm-up check on rank %d: %s" % (rank, exc), file=sys.stderr)
+                bad = 1.0
+            flag = torch.tensor([bad], device="cuda")
+            ctx.dist.all_reduce(flag, op=ctx.dist.ReduceOp.MAX)
+            if float(flag.item()) != 0.0:
+                ctx.totals_via = "nccl"                    # every rank falls back together
         ctx.barrier()
         sampler.mark("timed_start")
         t0, t1 = ctx.event(), ctx.event()
@@ -970,7 +1018,13 @@ def main():
             "kernels_per_gpu": sw.khi - sw.klo, "queries_per_gpu_and_predictor": nq, "destinations": WAVE_D,
             "l2": "a 256 MB buffer is overwritten before every step, so no step finds its records or its "
                   "outputs of the step before in the 126 MB L2",
-            "collective": "two all-reduces per step (float64 [6] and [24]) over NCCL" if world > 1 else "none",
+            "collective": {"none": "none",
+                           "nccl": "two NCCL all-reduces per step (float64 [6] and [24])",
+                           "peer": "the final stage of every reduction stores its totals into mailboxes in the peer "
+                                   "GPUs' memory and adds up what the peers stored (five exchanges per step: [6] pair "
+                                   "totals, 4 x [6] query totals), checked against NCCL all-reduces in the warm-up"
+                           }[ctx.totals_via],
+            "peer_vs_nccl_max_rel_diff": exchange_check,
             "wave_phase_ms_per_step": w_ms / steps, "mlp_phase_ms_per_step": m_ms / steps,
             "e2e": "the rank's shard from pinned host memory through the host pipelines: one 20 B/kernel block up "
                    "and the predicted times (4 B/pair) down per 1,048,576-kernel chunk; features up (4 F + 1 B per "
@@ -1062,6 +1116,8 @@ def main():
         print(json.dumps(line), flush=True)
     # the other ranks wait for rank 0's host work on a socket, not in a NCCL barrier on their GPUs
     ctx.hd.host_barrier()
+    if ctx.peer is not None:
+        ctx.peer.close()
     if world > 1:
         ctx.dist.destroy_process_group()
 

@@ -106,6 +106,21 @@ EXPORTS = {
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
     "hb_mlp_inject_status": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_int32]),
     "hb_bounds_check_word": (ctypes.c_int32, [ctypes.POINTER(ctypes.c_uint32), ctypes.c_int32]),
+    "hb_peer_create": (ctypes.c_int32, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int32]),
+    "hb_peer_export": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_void_p]),
+    "hb_peer_connect": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_void_p]),
+    "hb_peer_connect_pointers": (ctypes.c_int32, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "hb_peer_mailbox": (ctypes.c_void_p, [ctypes.c_void_p]),
+    "hb_peer_set_wait_ns": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_int64]),
+    "hb_peer_destroy": (None, [ctypes.c_void_p]),
+    "hb_peer_status": (ctypes.c_int32, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]),
+    "hb_plane_sum_allreduce": (ctypes.c_int32, [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "hb_group_sum_allreduce": (ctypes.c_int32, [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p,
+        ctypes.c_void_p]),
+    "hb_peer_allreduce": (ctypes.c_int32, [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]),
 }
 
 _lib = None

@@ -16,7 +16,7 @@ OBJ_DIR = os.path.join(PKG_DIR, "_lib", "obj")
 INCLUDE_DIR = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(LIB_DIR, "libhabitat_b200.so")
 
-SOURCES = ["hb_error.cu", "wave_scale.cu", "reduce.cu", "mlp_chain.cu", "device_probe.cu"]
+SOURCES = ["hb_error.cu", "wave_scale.cu", "reduce.cu", "peer_exchange.cu", "mlp_chain.cu", "device_probe.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

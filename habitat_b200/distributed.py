@@ -6,8 +6,10 @@ totals: one all-reduce (sums per destination) or one all-gather (per-iteration
 totals) per batch, a few KB over NCCL.  The reference has no counterpart: its
 prediction path is a single host thread.
 """
+import ctypes
 import os
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -96,3 +98,98 @@ def sharded_totals(n_items, compute_totals, rank=None, world=None, align=4):
         world = dist.get_world_size() if dist.is_initialized() else 1
     lo, hi = shard_bounds_aligned(n_items, rank, world, align)
     return allreduce_sum_(compute_totals(lo, hi))
+
+
+class PeerTotals:
+    """Totals summed across the GPUs of one box inside the reduction kernels themselves.
+
+    plane_sum / group_sum work like their namesakes in `batched`, but the final stage of the
+    reduction also writes its results into a mailbox on every peer GPU and adds up what the
+    peers wrote (csrc/peer_exchange.cu), so the result is the sum over all ranks, identical on
+    every rank, without a separate collective launch.  Create one per process after the process
+    group is up (the mailbox handles travel through it); every rank must make the same calls in
+    the same order on one stream.  With one rank it degenerates to the local sums."""
+
+    def __init__(self, rank=None, world=None, connect=True):
+        from habitat_b200 import _native
+        self._native = _native
+        lib = _native.load()
+        if rank is None:
+            rank = dist.get_rank() if dist.is_initialized() else 0
+            world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank, self.world = rank, world
+        self._handle = ctypes.c_void_p(0)
+        if world == 1 or not connect:
+            _native.check(lib.hb_peer_create(ctypes.byref(self._handle), rank, world))
+            return
+        # Every rank goes through the same collectives whether or not its own set-up worked, and
+        # all ranks reach the same verdict: nobody is left waiting for a rank that gave up.
+        g = host_group()
+        mine, error = b"", None
+        try:
+            _native.check(lib.hb_peer_create(ctypes.byref(self._handle), rank, world))
+            buf = (ctypes.c_uint8 * 64)()
+            _native.check(lib.hb_peer_export(self._handle, buf))
+            mine = bytes(buf)
+        except Exception as exc:                           # noqa: BLE001 - reported to every rank below
+            error = exc
+        every = [None] * world
+        dist.all_gather_object(every, mine, group=g)
+        if all(len(b) == 64 for b in every):
+            try:
+                blob = (ctypes.c_uint8 * (64 * world)).from_buffer_copy(b"".join(every))
+                _native.check(lib.hb_peer_connect(self._handle, blob))
+            except Exception as exc:                       # noqa: BLE001
+                error = exc
+        verdicts = [None] * world
+        dist.all_gather_object(verdicts, error is None and all(len(b) == 64 for b in every), group=g)
+        if not all(verdicts):
+            self.close()
+            raise RuntimeError("peer exchange could not be set up on rank(s) %s%s" % (
+                [r for r, v in enumerate(verdicts) if not v], ": %s" % error if error else ""))
+        # every rank has mapped every mailbox before anyone writes
+
+    def connect_local(self, others):
+        """Wires up handles that live in this process on this GPU (tests: ranks walked through
+        one after the other).  `others`: all PeerTotals of the group in rank order."""
+        ptrs = (ctypes.c_void_p * self.world)(*[self._native.load().hb_peer_mailbox(o._handle) for o in others])
+        self._native.check(self._native.load().hb_peer_connect_pointers(self._handle, ptrs))
+
+    def plane_sum(self, values, out=None):
+        """Sum over all ranks of each row of a [P, L] float32 CUDA tensor (NaN skipped) -> [P] float64."""
+        P, L = values.shape
+        if out is None:
+            out = torch.empty((P,), dtype=torch.float64, device=values.device)
+        self._native.check(self._native.load().hb_plane_sum_allreduce(
+            self._handle, ctypes.c_void_p(values.data_ptr()), L, P, ctypes.c_void_p(out.data_ptr()),
+            self._native.current_stream_ptr()))
+        return out
+
+    def group_sum(self, values, keys, n_groups, out=None):
+        """Sum over all ranks of a float32 CUDA vector grouped by a uint8 key -> [n_groups] float64."""
+        if out is None:
+            out = torch.empty((n_groups,), dtype=torch.float64, device=values.device)
+        self._native.check(self._native.load().hb_group_sum_allreduce(
+            self._handle, ctypes.c_void_p(values.data_ptr()), ctypes.c_void_p(keys.data_ptr()), values.numel(),
+            n_groups, ctypes.c_void_p(out.data_ptr()), self._native.current_stream_ptr()))
+        return out
+
+    def allreduce_(self, values, phase=3):
+        """In-place sum over ranks of a float64 CUDA vector of at most 64 entries."""
+        self._native.check(self._native.load().hb_peer_allreduce(
+            self._handle, ctypes.c_void_p(values.data_ptr()), values.numel(), phase,
+            self._native.current_stream_ptr()))
+        return values
+
+    def set_wait(self, seconds):
+        self._native.check(self._native.load().hb_peer_set_wait_ns(self._handle, int(seconds * 1e9)))
+
+    def check_status(self):
+        """Synchronises and raises if a wait for a peer ran out."""
+        code = ctypes.c_int32(0)
+        self._native.check(self._native.load().hb_peer_status(self._handle, ctypes.byref(code)))
+
+    def close(self):
+        if self._handle:
+            self._native.load().hb_peer_destroy(self._handle)
+            self._handle = ctypes.c_void_p(0)

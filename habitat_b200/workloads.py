@@ -152,12 +152,13 @@ def torch_init_mlp_weights(op, seed=None, layers=8, width=1024):
 
 
 # ---------------------------------------------------------------------------
-# The fixed batch of the scale sweep: 67,108,864 (kernel, destination) pairs = 11,184,811 kernels
-# x 6 destinations (the last kernel rounds the pair count up by two) and 4,194,304 queries for
-# each of the four predictors.  Records are generated in chunks of 262,144 from per-chunk seeds,
+# The fixed batch of the scale sweep: 67,108,864 (kernel, destination) pairs rounded up to whole
+# kernels and to an even number of them = 11,184,812 kernels x 6 destinations (eight pairs of
+# padding; an even count keeps every output plane on an 8-byte boundary) and 4,194,304 queries
+# for each of the four predictors.  Records are generated in chunks of 262,144 from per-chunk seeds,
 # so any rank can produce exactly its shard [lo, hi) without generating the rest.
 # ---------------------------------------------------------------------------
-SWEEP_KERNELS = 11_184_811
+SWEEP_KERNELS = 11_184_812
 SWEEP_QUERIES = 4_194_304
 SWEEP_OPS = ("conv2d", "linear", "bmm", "lstm")
 SWEEP_CHUNK = 1 << 18

@@ -314,6 +314,54 @@ hb_status hb_group_sum(const float* values, const uint8_t* keys, int64_t n, int3
 hb_status hb_plane_sum_static(const float* values, int64_t plane_len, int32_t n_planes, double* out,
                               void* stream);
 
+/* ------------------------------------------------------------------------ */
+/* Totals across the GPUs of one box                                        */
+/* ------------------------------------------------------------------------ */
+
+/* Kernels and queries shard across GPUs with nothing to exchange but totals (a
+ * few float64 numbers per batch).  hb_plane_sum_allreduce / hb_group_sum_allreduce
+ * are hb_plane_sum / hb_group_sum whose final stage also exchanges the results:
+ * it stores them into a mailbox in every peer GPU's memory (plain stores through
+ * peer-mapped pointers, no multicast), waits for the peers' values in its own
+ * mailbox and adds them in rank order, so `out` holds the same sum, bit for bit,
+ * on every GPU.  One process per GPU; every rank makes the same calls in the same
+ * order, and the calls of a handle are ordered on its GPU (one stream, or events).
+ * At most 64 values per call (hb_group_sum_allreduce: 8 groups).
+ * Every device-side wait is bounded (1 s unless hb_peer_set_wait_ns says
+ * otherwise): when a peer does not show up the value becomes NaN, the kernel
+ * returns and hb_peer_status reports HB_ERR_DEVICE_TIMEOUT with the rank and value
+ * waited for; ranks should therefore meet on the host once before their first
+ * exchange.  Set-up: hb_peer_create on every rank (allocates the mailbox and the
+ * scratch; before any stream capture), hb_peer_export -> 64 bytes that every
+ * other rank passes, in rank order, to hb_peer_connect (CUDA IPC; the bytes
+ * travel by whatever channel the host has).  The reference has no counterpart:
+ * its totals are sums in one host process (analyzer/habitat/analysis/trace.py:26-36). */
+typedef struct hb_peer hb_peer;
+
+hb_status hb_peer_create(hb_peer** handle, int32_t rank, int32_t world);
+hb_status hb_peer_export(hb_peer* handle, uint8_t out[64]);
+/* handles: world x 64 bytes in rank order (this rank's own entry is ignored). */
+hb_status hb_peer_connect(hb_peer* handle, const uint8_t* handles);
+/* Same with device pointers that already address the peers' mailboxes from this
+ * GPU (mailboxes[r] = hb_peer_mailbox of rank r, mapped by the caller; handles
+ * that live in one process on one GPU, as in single-GPU tests). */
+hb_status hb_peer_connect_pointers(hb_peer* handle, void* const* mailboxes);
+void* hb_peer_mailbox(hb_peer* handle);
+hb_status hb_peer_set_wait_ns(hb_peer* handle, int64_t wait_ns);
+void hb_peer_destroy(hb_peer* handle);
+/* Synchronises; HB_ERR_DEVICE_TIMEOUT (reported once, then cleared) when a wait ran out. */
+hb_status hb_peer_status(hb_peer* handle, int32_t* device_status);
+
+hb_status hb_plane_sum_allreduce(hb_peer* handle, const float* values, int64_t plane_len,
+                                 int32_t n_planes, double* out, void* stream);
+hb_status hb_group_sum_allreduce(hb_peer* handle, const float* values, const uint8_t* keys, int64_t n,
+                                 int32_t n_groups, double* out, void* stream);
+/* The exchange alone, in place on n device values.  phase 3 publishes and gathers in
+ * one kernel; phases 1 (publish) and 2 (gather what the last publish of every rank
+ * left) exist so that several ranks can be walked through one after the other on a
+ * single GPU, where kernels must not wait for one another. */
+hb_status hb_peer_allreduce(hb_peer* handle, double* values, int32_t n, int32_t phase, void* stream);
+
 /* Builds made with -DHB_BOUNDS_CHECK compare every table and element index of the
  * wave-scaling kernels with its bound; the first violation is recorded in a device
  * word (site << 24 | index, top bit set) and the access redirected, nothing traps.
