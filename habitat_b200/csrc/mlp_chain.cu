@@ -5,44 +5,44 @@
 // (mlp.py:258-261), fc1 + ReLU, `layers` x [Linear(1024,1024) + ReLU] and fc2
 // (mlp.py:17-109) run as ONE persistent kernel; activations never leave the SM.
 //
-// Formulation.  Each CTA owns a tile of TILE_Q queries and computes every layer
+// Formulation.  Two CTAs of a cluster own a tile of queries and compute every layer
 // transposed, H^T = W . X^T, so that
-//   A (M = 128 output features x K) = a weight tile, streamed from global/L2
-//                                     into a shared-memory ring by bulk async
-//                                     copies (TMA engine, mbarrier completion);
-//   B (N = TILE_Q queries x K)      = the activations, resident in shared memory
-//                                     in the K-major 128-byte-swizzled layout;
-//   D (128 lanes x TILE_Q columns)  = fp32 accumulators in tensor memory, one
-//                                     column block per 128-feature tile, so the
-//                                     whole layer output (1024 x TILE_Q) lives in
-//                                     TMEM until it is drained.
-// tcgen05.mma (kind::f16, bf16 inputs, fp32 accumulate) is issued by one elected
-// lane of a warp that walks the issue loop as a whole;
-// the epilogue warps read TMEM with tcgen05.ld, add the bias, apply ReLU, round
-// to bf16 and overwrite the activation buffer in place - legal because the
-// complete layer output is parked in TMEM before the first write.  fc2 is a dot
-// product over features (= TMEM lanes), reduced through shared memory.
+//   A (M = 256 output features x K) = weight tiles, streamed from global/L2 into a
+//                                     shared-memory ring by tiled TMA loads (mbarrier
+//                                     completion), half of the rows in each CTA;
+//   B (N = 128 columns x K)         = the activations, resident in shared memory
+//                                     (MN-major, 128-byte swizzle), half of the columns
+//                                     in each CTA;
+//   D (128 lanes x 128 columns)     = fp32 accumulators in tensor memory, one column
+//                                     block per 256-feature block, so the whole layer
+//                                     output lives in TMEM until it is drained.
+// tcgen05.mma.cta_group::2 (kind::f16, bf16 inputs, fp32 accumulate) is issued by one
+// elected lane of a warp that walks the issue loop as a whole; the epilogue warps read TMEM
+// with tcgen05.ld, add the bias, apply ReLU, round to bf16 and overwrite the activation
+// buffer in place while the tensor core works on the remaining blocks of the layer.  fc2 is
+// a dot product over features (= TMEM lanes), reduced through shared memory.
 //
 // fc1 has K = F + 4 <= 12.  Its inputs are the normalised features, which need
 // more than bf16's 8 bits, so both x and w are split into bf16 hi + lo parts and
 // the three products hi.hi + lo.hi + hi.lo are laid side by side along K
 // (3 (F+4) <= 36 of the 64 columns of one K block).
 //
-// Precision modes: HB_PRECISION_BF16 rounds hidden activations and weights to
-// bf16 (TILE_Q = 64); HB_PRECISION_BF16X3 keeps hi + lo parts of both and issues
-// the same three-product expansion for every hidden layer (TILE_Q = 32).
+// Precision modes: HB_PRECISION_BF16 rounds hidden activations and weights to bf16 (128
+// queries per tile); HB_PRECISION_BF16X3 keeps hi + lo parts of both (64 queries per tile,
+// the two parts of an activation side by side along N, the two parts of a weight tile in
+// one ring slot: see the comment at the kernel).
 //
-// Warp roles: warp 0 = TMEM allocation, warp 1 = barrier set-up + MMA issuer,
-// warps 2-5 = epilogue (one TMEM lane quadrant each), warps 6-11 = weight
-// producers.  Bulk copies issued by one thread complete one after the other
-// (measured: about 750 cycles each whatever their size), so the ring's slots
-// are dealt round-robin to several issuing warps to keep copies in flight.
-// Every mbarrier wait is bounded: when a wait runs out the kernel records a status word, all roles leave their loops, outstanding bulk
-// copies are waited for (bounded) and TMEM is released.
+// Warp roles: warp 0 = TMEM allocation, warp 1 = barrier set-up + MMA issuer (leader CTA),
+// warps 2-5 and 12-15 = two epilogue groups (one TMEM lane quadrant per warp), warps 6-11 =
+// weight producers.  Bulk copies issued by one thread complete one after the other (measured:
+// about 750 cycles each whatever their size), so each ring slot has its own issuing warp.
+// Every mbarrier wait is bounded: when a wait runs out the kernel records a status word, all
+// roles leave their loops, outstanding bulk copies are waited for (bounded) and TMEM is released.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -57,25 +57,7 @@ constexpr int kKBlk = 64;               // bf16 per 128-byte swizzle row
 constexpr int kNumMT = kWidth / kMTile; // 8
 constexpr int kNumKB = kWidth / kKBlk;  // 16
 constexpr int kTileBytes = kMTile * 128;// one weight tile image: 16 KB
-constexpr int kProducerWarps = 6;        // warps 6..11; one lane of each issues bulk copies
-constexpr int kThreads = 192 + 32 * kProducerWarps;
-constexpr int kEpiThreads = 128;
 constexpr int kMaxInFeat = 12;          // F + 4 (conv2d: 8 + 4)
-
-template <int TILE_Q, bool SPLIT>
-struct Cfg {
-  static constexpr int kActKbBytes = TILE_Q * 128;             // one K block of activations
-  static constexpr int kActBytes = kNumKB * kActKbBytes;       // hi (or only) copy
-  static constexpr int kActCopies = SPLIT ? 2 : 1;
-  static constexpr int kStageBytes = kTileBytes * (SPLIT ? 2 : 1);
-  static constexpr int kStages = SPLIT ? 3 : 6;
-  static constexpr int kBarBytes = 1024;
-  static constexpr int kSmemBytes =
-      kActBytes * kActCopies + kStages * kStageBytes + kBarBytes + 1024 /* alignment slack */;
-  static constexpr int kTmemCols = kNumMT * TILE_Q;            // 512 or 256
-  static_assert(kTmemCols == 512 || kTmemCols == 256, "TMEM allocation must be a power of two");
-  static_assert(kSmemBytes <= 232448, "over the 227 KB shared-memory limit");
-};
 
 struct MlpParams {
   const uint8_t* wpack;      // weight tile images, producer order
@@ -128,13 +110,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
-                                         uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -143,19 +118,6 @@ __device__ __forceinline__ void tc_fence_before() {
 }
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
 }
 __device__ __forceinline__ uint32_t elect_one() {
   uint32_t pred;
@@ -189,6 +151,21 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // 32 lanes x 64 consecutive 32-bit columns in one instruction: halves the number of
 // load round trips of the epilogue (each tcgen05.ld + wait costs several hundred cycles).
 __device__ __forceinline__ void tc_ld64(uint32_t taddr, float (&v)[64]) {
@@ -217,25 +194,6 @@ __device__ __forceinline__ void tc_ld64(uint32_t taddr, float (&v)[64]) {
   for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows are 128 B
-// apart, groups of 8 rows 1024 B apart (the stride byte offset); the leading
-// byte offset is unused for swizzled K-major operands; descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);  // start address
-  d |= static_cast<uint64_t>(1) << 16;                 // leading byte offset (16 B units)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;         // stride byte offset
-  d |= static_cast<uint64_t>(1) << 46;                 // version
-  d |= static_cast<uint64_t>(2) << 61;                 // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor: D = fp32, A = B = bf16, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t make_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-         (static_cast<uint32_t>(kMTile >> 4) << 24);
-}
-
 // Byte offset of element (row, col) inside a K-major 128-byte-swizzled block of
 // 128-byte rows: 16-byte chunks are permuted by the row index modulo 8.
 __host__ __device__ __forceinline__ uint32_t swz_off(uint32_t row, uint32_t col) {
@@ -262,289 +220,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-__device__ __forceinline__ void epi_bar_sync() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-}
-
 // ---------------------------------------------------------------------------
-// The kernel
-// ---------------------------------------------------------------------------
-template <int TILE_Q, bool SPLIT>
-__global__ void __launch_bounds__(kThreads, 1) mlp_chain_kernel(const __grid_constant__ MlpParams p) {
-  using C = Cfg<TILE_Q, SPLIT>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - raw);
-
-  const uint32_t act_hi = base;
-  const uint32_t act_lo = base + C::kActBytes;  // SPLIT only
-  const uint32_t stage0 = base + C::kActBytes * C::kActCopies;
-  const uint32_t bars = stage0 + C::kStages * C::kStageBytes;
-  uint8_t* bars_ptr = base_ptr + (bars - base);
-  // barrier block: full[stages], empty[stages], acc_full, act_ready, then words
-  const uint32_t bar_full = bars;
-  const uint32_t bar_empty = bars + 8 * C::kStages;
-  const uint32_t bar_acc = bars + 16 * C::kStages;
-  const uint32_t bar_act = bar_acc + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 16 * C::kStages + 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 16 * C::kStages + 20);
-  volatile int* epi_ok = reinterpret_cast<volatile int*>(bars_ptr + 16 * C::kStages + 24);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 32) {
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
-    }
-    mbar_init(bar_acc, 1);
-    mbar_init(bar_act, kEpiThreads);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_slot)),
-                 "r"(static_cast<uint32_t>(C::kTmemCols))
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  const int n_layers = p.layers + 1;  // fc1 + hidden
-  int my_tiles = 0;
-  if (static_cast<int>(blockIdx.x) < p.num_tiles)
-    my_tiles = (p.num_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1;
-
-  uint32_t issued = 0;  // producer: stage loads issued (for the drain at exit)
-
-  if (warp >= 6) {
-    // ------------------------------ producers -----------------------------
-    // Producer w takes loads w, w + S, w + 2S, ... (S ring slots) of the one global sequence
-    // (tile -> layer -> 128-feature block -> K block) the MMA issuer consumes.
-    // One producer per ring slot: a slot's loads are then issued in order by a
-    // single thread, which the parity protocol of its empty barrier needs.
-    static_assert(C::kStages <= kProducerWarps, "need one producer warp per ring slot");
-    if (lane == 0 && warp - 6 < C::kStages) {
-      const uint32_t w = static_cast<uint32_t>(warp - 6);
-      const uint32_t per_tile =
-          static_cast<uint32_t>(kNumMT + p.layers * kNumMT * kNumKB);
-      const uint32_t total = per_tile * static_cast<uint32_t>(my_tiles);
-      uint32_t it = w;
-      for (; it < total; it += C::kStages) {
-        const uint32_t s = it % C::kStages;
-        const uint32_t ph = (it / C::kStages) & 1u;
-        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 0x101)) break;
-        mbar_expect_tx(bar_full + 8 * s, C::kStageBytes);
-        bulk_g2s(stage0 + s * C::kStageBytes,
-                 p.wpack + static_cast<size_t>(it % per_tile) * C::kStageBytes, C::kStageBytes,
-                 bar_full + 8 * s);
-      }
-      issued = it;  // first sequence number this producer did not issue
-    }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ----------------------------
-    // The whole warp walks the loop and an elected lane issues (operands of tcgen05.mma
-    // are uniform registers; a loop run by one lane of a diverged warp issues slower).
-    {
-      constexpr uint32_t idesc = make_idesc(TILE_Q);
-      uint32_t it = 0, lay = 0;
-      bool ok = true;
-      for (int t = 0; t < my_tiles && ok; ++t) {
-        for (int L = 0; L < n_layers && ok; ++L, ++lay) {
-          if (!mbar_wait(bar_act, lay & 1u, abort_flag, p.status, 0x201)) { ok = false; break; }
-          tc_fence_after();
-          const int nkb = L == 0 ? 1 : kNumKB;
-          for (int mt = 0; mt < kNumMT && ok; ++mt) {
-            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(mt * TILE_Q);
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
-              const uint32_t s = it % C::kStages;
-              const uint32_t ph = (it / C::kStages) & 1u;
-              if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x202)) { ok = false; break; }
-              const uint32_t a_base = stage0 + s * C::kStageBytes;
-              const uint32_t b_base = act_hi + kb * C::kActKbBytes;
-              if (elect_one()) {
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                  const uint64_t a_hi = smem_desc_k128(a_base + ks * 32);
-                  const uint64_t b_hi = smem_desc_k128(b_base + ks * 32);
-                  tc_mma_bf16(d_tmem, a_hi, b_hi, idesc, (kb | ks) != 0 ? 1u : 0u);
-                  if (SPLIT && L > 0) {
-                    const uint64_t a_lo = smem_desc_k128(a_base + kTileBytes + ks * 32);
-                    const uint64_t b_lo = smem_desc_k128(act_lo + kb * C::kActKbBytes + ks * 32);
-                    tc_mma_bf16(d_tmem, a_hi, b_lo, idesc, 1u);
-                    tc_mma_bf16(d_tmem, a_lo, b_hi, idesc, 1u);
-                  }
-                }
-                tc_commit(bar_empty + 8 * s);  // frees the ring slot once these MMAs retire
-                if (mt == kNumMT - 1 && kb == nkb - 1) tc_commit(bar_acc);  // the whole layer sits in TMEM
-              }
-              __syncwarp();
-            }
-          }
-        }
-      }
-    }
-  } else if (warp >= 2) {
-    // ------------------------------ epilogue ------------------------------
-    const int e = threadIdx.x - 64;            // 0..127
-    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
-    const int r = quad * 32 + lane;            // feature row inside a 128-feature tile
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-    const int C_in = p.n_op_feat + 4;
-    uint32_t lay = 0;
-    bool ok = true;
-    float* red = reinterpret_cast<float*>(base_ptr);  // [128][TILE_Q + 1], aliases activations
-
-    for (int t = 0; t < my_tiles && ok; ++t) {
-      const int tile = static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x);
-      const int64_t q0 = static_cast<int64_t>(tile) * TILE_Q;
-
-      // ---- normalised, split input features -> K block 0 (mlp.py:258-261) ----
-      if (e < TILE_Q) {
-        const int64_t q = q0 + e;
-        __nv_bfloat16 row[kKBlk];
-#pragma unroll
-        for (int c = 0; c < kKBlk; ++c) row[c] = __float2bfloat16_rn(0.0f);
-        if (q < p.Q) {
-          int dr = p.dev_row[q];
-          dr = dr < p.n_dev ? dr : p.n_dev - 1;
-          for (int c = 0; c < C_in; ++c) {
-            const double x = c < p.n_op_feat
-                                 ? static_cast<double>(p.feats[q * p.n_op_feat + c])
-                                 : p.dev_feat[dr * 4 + (c - p.n_op_feat)];
-            const float xn = static_cast<float>((x - p.mu[c]) / p.sigma[c]);
-            const __nv_bfloat16 hi = __float2bfloat16_rn(xn);
-            const __nv_bfloat16 lo = __float2bfloat16_rn(xn - __bfloat162float(hi));
-            row[c] = hi;
-            row[C_in + c] = lo;
-            row[2 * C_in + c] = hi;
-          }
-        }
-        const uint4* src = reinterpret_cast<const uint4*>(row);
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          uint4* dst = reinterpret_cast<uint4*>(base_ptr + e * 128 + (((ch ^ e) & 7) << 4));
-          *dst = src[ch];
-        }
-      }
-      fence_proxy_async();
-      mbar_arrive(bar_act);
-
-      for (int L = 0; L < n_layers && ok; ++L, ++lay) {
-        // One thread waits and hands the verdict to the other 127 through the
-        // named barrier, so the whole group takes the same branch.
-        if (e == 0) *epi_ok = mbar_wait(bar_acc, lay & 1u, abort_flag, p.status, 0x301) ? 1 : 0;
-        epi_bar_sync();
-        if (*epi_ok == 0) { ok = false; break; }
-        tc_fence_after();
-        const float* bias = p.bias + L * kWidth;
-        const bool last = (L == n_layers - 1);
-        if (!last) {
-          // bias + ReLU + bf16, written back as the next layer's B operand
-#pragma unroll 1
-          for (int mt = 0; mt < kNumMT; ++mt) {
-            const float b = __ldg(bias + mt * kMTile + r);
-            const int f = mt * kMTile + r;                 // feature = K index of the next layer
-            const uint32_t kb_off = static_cast<uint32_t>(f >> 6) * C::kActKbBytes;
-            const uint32_t col = static_cast<uint32_t>(f & 63);
-#pragma unroll
-            for (int h = 0; h < TILE_Q / 32; ++h) {
-              float v[32];
-              tc_ld32(t_lane + static_cast<uint32_t>(mt * TILE_Q + h * 32), v);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const uint32_t n = static_cast<uint32_t>(h * 32 + i);
-                const float x = fmaxf(v[i] + b, 0.0f);
-                const __nv_bfloat16 hi = __float2bfloat16_rn(x);
-                const uint32_t off = kb_off + swz_off(n, col);
-                *reinterpret_cast<__nv_bfloat16*>(base_ptr + off) = hi;
-                if (SPLIT) {
-                  const __nv_bfloat16 lo = __float2bfloat16_rn(x - __bfloat162float(hi));
-                  *reinterpret_cast<__nv_bfloat16*>(base_ptr + C::kActBytes + off) = lo;
-                }
-              }
-            }
-          }
-          tc_fence_before();
-          fence_proxy_async();
-          mbar_arrive(bar_act);
-        } else {
-          // fc2 (mlp.py:46-48): dot over features = over TMEM lanes and tiles
-          float acc[TILE_Q];
-#pragma unroll
-          for (int i = 0; i < TILE_Q; ++i) acc[i] = 0.0f;
-#pragma unroll 1
-          for (int mt = 0; mt < kNumMT; ++mt) {
-            const float b = __ldg(bias + mt * kMTile + r);
-            const float w = __ldg(p.fc2_w + mt * kMTile + r);
-#pragma unroll
-            for (int h = 0; h < TILE_Q / 32; ++h) {
-              float v[32];
-              tc_ld32(t_lane + static_cast<uint32_t>(mt * TILE_Q + h * 32), v);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) acc[h * 32 + i] = fmaf(w, fmaxf(v[i] + b, 0.0f), acc[h * 32 + i]);
-            }
-          }
-          tc_fence_before();
-          // every MMA of this tile has retired, so the activation buffer is free
-#pragma unroll
-          for (int i = 0; i < TILE_Q; ++i) red[r * (TILE_Q + 1) + i] = acc[i];
-          epi_bar_sync();
-          {
-            const int n = e % TILE_Q;
-            const int part = e / TILE_Q;               // 128 / TILE_Q partial sums per query
-            constexpr int kParts = kEpiThreads / TILE_Q;
-            constexpr int kRows = kMTile / kParts;
-            float s = 0.0f;
-            for (int j = 0; j < kRows; ++j) s += red[(part * kRows + j) * (TILE_Q + 1) + n];
-            epi_bar_sync();                            // all reads of `red` done
-            red[part * TILE_Q + n] = s;
-            epi_bar_sync();
-            if (e < TILE_Q) {
-              float tot = p.fc2_b;
-              for (int j = 0; j < kParts; ++j) tot += red[j * TILE_Q + e];
-              const int64_t q = q0 + e;
-              if (q < p.Q) p.out[q] = tot;
-            }
-            epi_bar_sync();                            // `red` may be overwritten again
-          }
-        }
-      }
-    }
-  }
-
-  // ------------------------------ teardown ------------------------------
-  tc_fence_before();
-  __syncthreads();
-  if (warp >= 6 && lane == 0 && *abort_flag) {
-    // a role gave up: wait (bounded) for this producer's last copy to land
-    if (warp - 6 < C::kStages && issued >= static_cast<uint32_t>(C::kStages)) {
-      const uint32_t j = issued - C::kStages;
-      const uint32_t s = j % C::kStages, ph = (j / C::kStages) & 1u;
-      const long long t0 = clock64();
-      while (!mbar_try_wait(bar_full + 8 * s, ph)) {
-        if (clock64() - t0 > kWaitCycles) break;
-      }
-    }
-  }
-  __syncthreads();
-  if (warp == 0) {
-    __syncwarp();
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(static_cast<uint32_t>(C::kTmemCols))
-                 : "memory");
-  }
-}
-
-// ---------------------------------------------------------------------------
-// Two-CTA form (bf16 mode).  A single CTA can only keep 64 queries on chip,
+// The kernel.  A single CTA can only keep 64 queries on chip,
 // and an M = 128 MMA with N = 64 occupies the tensor core for the same 64 cycles
 // as one with N = 128, so the one-CTA kernel tops out at half rate.  Here two
 // CTAs of a cluster share one tile of 128 queries:
@@ -700,8 +377,22 @@ __device__ __forceinline__ void tc_mma_pair_bf16(uint32_t d_tmem, uint64_t a_des
       : "memory");
 }
 
+// SPLIT = false: bf16 operands, 128 queries per cluster tile (64 per CTA).
+// SPLIT = true (the 1e-4 mode): activations and weights are kept as bf16 hi + lo parts.  A CTA
+// holds 32 queries and lays the hi and lo parts of an activation side by side along N (the 128-byte
+// B row of K index k is [hi of 32 queries | lo of 32 queries]), so the same M = 256, N = 128 MMA
+// multiplies a weight tile with both parts at once, at full rate; a ring slot carries the hi and the
+// lo image of one K block of weights and both accumulate into the same TMEM columns:
+// D = (W_hi + W_lo) [x_hi | x_lo], and the epilogue adds the two column halves of a query (all four
+// partial products, fp32 accumulation).  Two MMAs per K step and 64 queries instead of one and 128:
+// a quarter of the bf16 rate.
+template <bool SPLIT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
+  constexpr int kTileQ = SPLIT ? kPairQ / 2 : kPairQ;          // queries per cluster tile
+  constexpr int kHalfQ = kTileQ / 2;                           // queries per CTA
+  constexpr int kLoadsPerUnit = SPLIT ? 4 : 4 / kPairSlotKb;   // ring slots per (block, K quarter) unit
+  constexpr int kRowsPerImage = (SPLIT ? 2 : 1) * (kTileBytes / 128);   // 128-byte rows per packed K block
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -784,7 +475,7 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
           // A ring slot takes two consecutive K blocks of one output block (fc1 has only one);
           // a hidden layer is streamed as 16 (block, K quarter) units of two slots each.
           const int n_units = nkb == 1 ? kPairMT : 16;
-          const int n_loads = nkb == 1 ? 1 : 4 / kPairSlotKb;
+          const int n_loads = nkb == 1 ? 1 : kLoadsPerUnit;
           const uint32_t load_bytes = nkb == 1 ? kTileBytes : kPairStageBytes;
           {
             for (int u = 0; u < n_units && ok; ++u) {
@@ -799,8 +490,11 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
                 const long long q1 = ptimed ? clock64() : 0;
                 // both CTAs' boxes are counted on the leader's barrier
                 if (rank == 0) mbar_expect_tx(bar_full + 8 * w, 2 * load_bytes);
+                // bf16: a slot takes two consecutive K blocks (16 KB images); split: the hi and lo
+                // image of one K block (stored back to back)
                 tma_rows_2sm(stage0 + w * kPairStageBytes, nkb == 1 ? &p.tmap_tile : &p.tmap_slot,
-                             static_cast<int32_t>((blk + kPairSlotKb * g) * (kTileBytes / 128)), peer_full_leader);
+                             static_cast<int32_t>((blk + (SPLIT ? 1 : kPairSlotKb) * g) * kRowsPerImage),
+                             peer_full_leader);
                 issued = it + 1;
                 if (ptimed) {
                   mbar_wait(bar_full + 8 * w, ph, abort_flag, p.status, 0x112);
@@ -848,7 +542,7 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
         for (int L = 0; L < n_layers && ok; ++L) {
           const int nkb = L == 0 ? 1 : kNumKB;
           const int n_units = nkb == 1 ? kPairMT : 16;
-          const int n_loads = nkb == 1 ? 1 : 4 / kPairSlotKb;
+          const int n_loads = nkb == 1 ? 1 : kLoadsPerUnit;
           // fc1 reads K block 0, written after the previous tile's TMEM was read out
           if (nkb == 1 && !wait_flip(bar_actq, 0, 0, mc_act, 0x211)) { ok = false; break; }
           uint32_t seen = 0;   // bits 0-3: K quarters used, bits 4-7: blocks written, bits 8-15: units done per block
@@ -872,7 +566,8 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
               if (!mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, 0x212)) { ok = false; break; }
               const long long m2 = mtimed ? clock64() : 0;
               const uint64_t a0 = desc_hi | (a_lo0 + s * (kPairStageBytes >> 4));
-              const uint64_t b0 = desc_hi | (b_lo0 + static_cast<uint32_t>(kq * 4 + kPairSlotKb * g) * (kPairActKb >> 4));
+              const uint64_t b0 = desc_hi | (b_lo0 + static_cast<uint32_t>(kq * 4 + (SPLIT ? 1 : kPairSlotKb) * g) *
+                                                         (kPairActKb >> 4));
               if (elect_one()) {
                 // a K step of 16: 32 bytes along an A row, 16 K rows (2 KB) of B
                 tc_mma_pair_bf16(d_tmem, a0, b0, idesc, (first_of_block && g == 0) ? 0u : 1u);
@@ -880,8 +575,9 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
                 tc_mma_pair_bf16(d_tmem, a0 + 4, b0 + 256, idesc, 1u);
                 tc_mma_pair_bf16(d_tmem, a0 + 6, b0 + 384, idesc, 1u);
                 if (kPairSlotKb == 2 && nkb > 1) {
-                  // second K block of the slot: next weight tile (16 KB on), next 64 K rows (8 KB on)
-                  const uint64_t a1 = a0 + (kTileBytes >> 4), b1 = b0 + (kPairActKb >> 4);
+                  // second image of the slot (16 KB on): bf16: the next K block, i.e. the next 64 K rows
+                  // of the activations (8 KB on); split: the lo part of the same K block, same activations
+                  const uint64_t a1 = a0 + (kTileBytes >> 4), b1 = SPLIT ? b0 : b0 + (kPairActKb >> 4);
                   tc_mma_pair_bf16(d_tmem, a1, b1, idesc, 1u);
                   tc_mma_pair_bf16(d_tmem, a1 + 2, b1 + 128, idesc, 1u);
                   tc_mma_pair_bf16(d_tmem, a1 + 4, b1 + 256, idesc, 1u);
@@ -932,14 +628,16 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
 
     for (int t = 0; t < my_tiles && ok; ++t, ++tile_no) {
       const int tile = pair_id + t * n_pairs;
-      const int64_t q0 = static_cast<int64_t>(tile) * kPairQ + static_cast<int64_t>(rank) * kPairHalfQ;
+      const int64_t q0 = static_cast<int64_t>(tile) * kTileQ + static_cast<int64_t>(rank) * kHalfQ;
 
       if (T < kPairHalfQ) {
+        // one B column per thread: a query's split features (SPLIT: columns 32..63 are the lo parts
+        // of the hidden layers; fc1 carries its own hi/lo expansion along K, so they are zero here)
         const int64_t q = q0 + T;
         __nv_bfloat16 row[kKBlk];
 #pragma unroll
         for (int c = 0; c < kKBlk; ++c) row[c] = __float2bfloat16_rn(0.0f);
-        if (q < p.Q) {
+        if (T < kHalfQ && q < p.Q) {
           int dr = p.dev_row[q];
           dr = dr < p.n_dev ? dr : p.n_dev - 1;
           for (int c = 0; c < C_in; ++c) {
@@ -1011,13 +709,26 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
                   else mbar_arrive_remote(bar_tfree_leader);
                 }
               }
+              if (SPLIT) {
+                // columns 0..31 hold W x_hi, 32..63 W x_lo of the same 32 queries: add them, then split
+                // the activation into bf16 hi (columns 0..31 of the new row) and lo (32..63)
 #pragma unroll
-              for (int g = 0; g < 8; ++g) {          // eight queries per 16-byte store
+                for (int i = 0; i < 32; ++i) {
+                  const float x = fmaxf((v[i] + v[32 + i]) + b, 0.0f);
+                  const float hi = __bfloat162float(__float2bfloat16_rn(x));
+                  v[i] = hi;
+                  v[32 + i] = x - hi;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i] + b, 0.0f);
+              }
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {          // eight values per 16-byte store
                 uint32_t w4[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                  const __nv_bfloat162 pk = __floats2bfloat162_rn(fmaxf(v[g * 8 + 2 * u] + b, 0.0f),
-                                                                  fmaxf(v[g * 8 + 2 * u + 1] + b, 0.0f));
+                  const __nv_bfloat162 pk = __floats2bfloat162_rn(v[g * 8 + 2 * u], v[g * 8 + 2 * u + 1]);
                   w4[u] = *reinterpret_cast<const uint32_t*>(&pk);
                 }
                 const uint32_t off = row_off + ((static_cast<uint32_t>(g) ^ sw) << 4);
@@ -1046,9 +757,10 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
           if (epi_ok[0] == 0) { ok = false; break; }
           tc_fence_after();
           const long long c1 = timed ? clock64() : 0;
-          // fc2 over this CTA's 512 features, 32 queries at a time
+          // fc2 over this CTA's 512 features, 32 queries at a time (bf16: the four column quarters
+          // of the 128 queries; split: the two CTAs' 32 queries, hi and lo columns added first)
 #pragma unroll 1
-          for (int qd = 0; qd < 4; ++qd) {
+          for (int qd = 0; qd < (SPLIT ? 2 : 4); ++qd) {
             float acc[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
@@ -1058,10 +770,22 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
               const int f = j * 256 + static_cast<int>(rank) * 128 + r;
               const float b = __ldg(bias + f);
               const float w = __ldg(p.fc2_w + f);
-              float v[32];
-              tc_ld32(t_lane + static_cast<uint32_t>(j * kPairQ + qd * 32), v);
+              if (SPLIT) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) acc[i] = fmaf(w, fmaxf(v[i] + b, 0.0f), acc[i]);
+                for (int h = 0; h < 2; ++h) {
+                  float vh[16], vl[16];
+                  tc_ld16(t_lane + static_cast<uint32_t>(j * kPairQ + qd * 64 + h * 16), vh);
+                  tc_ld16(t_lane + static_cast<uint32_t>(j * kPairQ + qd * 64 + 32 + h * 16), vl);
+#pragma unroll
+                  for (int i = 0; i < 16; ++i)
+                    acc[h * 16 + i] = fmaf(w, fmaxf((vh[i] + vl[i]) + b, 0.0f), acc[h * 16 + i]);
+                }
+              } else {
+                float v[32];
+                tc_ld32(t_lane + static_cast<uint32_t>(j * kPairQ + qd * 32), v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] = fmaf(w, fmaxf(v[i] + b, 0.0f), acc[i]);
+              }
             }
             const int row = grp * 128 + r;
 #pragma unroll
@@ -1077,8 +801,10 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
               float tot = 0.0f;
 #pragma unroll
               for (int k2 = 0; k2 < 8; ++k2) tot += red[k2 * 32 + T];
-              const int slot = (qd & 1) * 32 + T;      // index among the owner's 64 queries
-              if (static_cast<uint32_t>(qd >> 1) == rank) fc2_mine[slot] = tot;
+              // index among the owner's queries, and which CTA owns them
+              const int slot = SPLIT ? T : (qd & 1) * 32 + T;
+              const uint32_t owner = static_cast<uint32_t>(SPLIT ? qd : qd >> 1);
+              if (owner == rank) fc2_mine[slot] = tot;
               else st_cluster_f32(map_to_cta(smem_u32(fc2_peer + slot), peer), tot);
             }
             pair_epi_bar_sync();
@@ -1091,7 +817,7 @@ mlp_chain_pair_kernel(const __grid_constant__ MlpParams p) {
           }
           pair_epi_bar_sync();
           if (epi_ok[0] == 0) { ok = false; break; }
-          if (T < kPairHalfQ) {
+          if (T < kHalfQ) {
             const int64_t q = q0 + T;
             if (q < p.Q) p.out[q] = fc2_mine[T] + fc2_peer[T] + p.fc2_b;
           }
@@ -1292,11 +1018,11 @@ extern "C" hb_status hb_mlp_create(hb_mlp** handle, int32_t n_op_features, int32
   if ((e = cudaMalloc(reinterpret_cast<void**>(&h->phase_cycles), 16 * sizeof(long long))) != cudaSuccess)
     return fail(e, "cudaMalloc phase_cycles");
   if ((e = cudaMemset(h->phase_cycles, 0, 16 * sizeof(long long))) != cudaSuccess) return fail(e, "cudaMemset");
-  e = cudaFuncSetAttribute(mlp_chain_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  e = cudaFuncSetAttribute(mlp_chain_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kPairSmemBytes);
   if (e != cudaSuccess) return fail(e, "cudaFuncSetAttribute");
-  e = cudaFuncSetAttribute(mlp_chain_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           Cfg<32, true>::kSmemBytes);
+  e = cudaFuncSetAttribute(mlp_chain_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kPairSmemBytes);
   if (e != cudaSuccess) return fail(e, "cudaFuncSetAttribute");
   *handle = h;
   return HB_OK;
@@ -1317,7 +1043,7 @@ extern "C" hb_status hb_mlp_predict(hb_mlp* h, const float* op_features, const u
     return HB_ERR_INVALID_ARGUMENT;
   }
   const bool split = h->precision == HB_PRECISION_BF16X3;
-  const int tile_q = split ? 32 : kPairQ;
+  const int tile_q = split ? kPairQ / 2 : kPairQ;
   const int64_t tiles = (Q + tile_q - 1) / tile_q;
   if (tiles > 0x7FFFFFFF) {
     hb::set_error("hb_mlp_predict: Q too large for one launch");
@@ -1334,14 +1060,10 @@ extern "C" hb_status hb_mlp_predict(hb_mlp* h, const float* op_features, const u
   p.unit_order = kPairOrder;
   p.unit_gates = kPairGates;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (split) {
-    const int grid = static_cast<int>(tiles < h->sm_count ? tiles : h->sm_count);
-    mlp_chain_kernel<32, true><<<grid, kThreads, Cfg<32, true>::kSmemBytes, s>>>(p);
-  } else {
-    // one cluster of two CTAs per tile of 128 queries, at most one cluster per SM pair
-    const int pairs = static_cast<int>(tiles < h->sm_count / 2 ? tiles : h->sm_count / 2);
-    mlp_chain_pair_kernel<<<2 * pairs, kPairThreads, kPairSmemBytes, s>>>(p);
-  }
+  // one cluster of two CTAs per tile (128 queries, 64 in split precision), at most one cluster per SM pair
+  const int pairs = static_cast<int>(tiles < h->sm_count / 2 ? tiles : h->sm_count / 2);
+  if (split) mlp_chain_pair_kernel<true><<<2 * pairs, kPairThreads, kPairSmemBytes, s>>>(p);
+  else mlp_chain_pair_kernel<false><<<2 * pairs, kPairThreads, kPairSmemBytes, s>>>(p);
   HB_CUDA_TRY(cudaGetLastError());
   return HB_OK;
 }

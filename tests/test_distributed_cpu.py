@@ -73,3 +73,33 @@ def test_two_rank_totals_match_one_rank(tmp_path):
     assert np.allclose(got, want, rtol=1e-12)
     gathered = np.load(tmp_path / "gathered.npy")
     assert gathered.shape == (5, 3) and (gathered[:2] == 0).all() and (gathered[2:] == 1).all()
+
+
+def _peer_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    from habitat_b200 import distributed as hdist
+    hdist.init("gloo")
+    # no GPU here: creating the mailbox fails on every rank.  Every rank must still walk through
+    # the same collectives and come out with the same verdict instead of waiting for the others.
+    try:
+        hdist.PeerTotals()
+        verdict = "created"
+    except RuntimeError as exc:
+        verdict = "refused: %s" % exc
+    hdist.host_barrier()
+    with open(os.path.join(out_dir, "peer%d.txt" % rank), "w") as f:
+        f.write(verdict)
+    torch.distributed.destroy_process_group()
+
+
+def test_peer_setup_fails_on_every_rank_together(tmp_path):
+    if torch.cuda.is_available():
+        pytest.skip("exercises the no-GPU failure path")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_peer_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    texts = [open(tmp_path / ("peer%d.txt" % r)).read() for r in range(2)]
+    assert all(t.startswith("refused: peer exchange could not be set up on rank(s) [0, 1]") for t in texts), texts

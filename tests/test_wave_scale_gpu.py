@@ -294,3 +294,21 @@ print("checked build ok")
     from habitat_b200 import _native
     import ctypes
     assert _native.load().hb_bounds_check_word(ctypes.byref(ctypes.c_uint32(0)), 0) == _native.HB_ERR_UNSUPPORTED
+
+
+def test_second_gpu_gets_its_own_tables(bench_devices):
+    """One process, two GPUs: the device table and the reduction scratch are kept per GPU, so a
+    launch with the other GPU current reads that GPU's own copy (uploaded at its first use)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    kernels = workloads.make_kernels(6000, seed=91)
+    ref = run_wave_oracle(kernels, bench_devices[0], bench_devices)
+    for dev in (0, 1, 0):
+        with torch.cuda.device(dev):
+            got = run_wave_gpu(kernels, bench_devices[0], bench_devices)
+            assert got["fast_path"] == "wave_scale_lut_kernel"
+            assert_wave_equal(got, ref)
+            res = batched.wave_scale(batched.KernelBatch.from_numpy(kernels, device="cuda:%d" % dev),
+                                     bench_devices[0], bench_devices)
+            tot = batched.plane_sum(res.scaled_ns).cpu().numpy()
+            assert np.allclose(tot, np.nansum(to_numpy(res.scaled_ns).astype(np.float64), axis=1), rtol=1e-12)
