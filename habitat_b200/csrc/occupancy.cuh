@@ -13,6 +13,7 @@
 // into an hb_dev_pre; the per-kernel part is hb_occupancy().
 #pragma once
 
+#include <cmath>
 #include <cstdint>
 
 #include "habitat_b200.h"
@@ -342,4 +343,86 @@ inline FastDev fold_fast(const hb_device_spec& s, const hb_dev_pre& pre) {
   f.num_sms = s.num_sms;
   f.sms_magic = magic_of(static_cast<uint32_t>(s.num_sms));
   return f;
+}
+
+// ---------------------------------------------------------------------------
+// Tables of the table kernel (wave_scale.cu: wave_scale_lut_kernel), built on the host
+// ---------------------------------------------------------------------------
+// Per device row, one byte each:
+//   P[warps per block 0..33][256-register units per warp 0..33] = min(register, warp and
+//     blocks-per-SM limit)          (index 33 = "more than 32 warps" / "more than 256 registers")
+//   S[shared memory in 128-byte steps 0..2047] = shared-memory limit (last entry: above every cap)
+// and per occupancy 0..32 an entry T = {M, sh, A_hi, A_lo}: floor(n / (SMs * occ)) =
+// umulhi(n, M) >> sh for every 0 <= n < 2^31, A = log2(occ) - log2(clock MHz) as float hi + lo.
+constexpr int kLutW = 34;
+constexpr int kLutU = 34;
+constexpr int kLutP = kLutW * kLutU;
+constexpr int kLutS = 2048;
+constexpr int kLutOcc = 33;
+
+struct alignas(16) LutOcc {
+  uint32_t magic, shift;
+  float lg_hi, lg_lo;
+};
+
+// Whether a row can be tabulated.
+inline bool lut_row_ok(const hb_device_spec& s, const hb_dev_pre& pre) {
+  return fast_row_ok(s, pre) && s.num_sms >= 2 && pre.max_threads_per_block % 32 == 0 &&
+         pre.max_threads_per_block <= 1024 && pre.smem_reserved % 128 == 0 &&
+         pre.smem_cap <= (kLutS - 2) * 128 && pre.blocks_limit <= kLutOcc - 1 && s.base_clock_mhz > 0;
+}
+
+// Tabulates one device row.  `magic`: magic_of(i) for i < kMagicN.
+inline void build_row_lut(const hb_device_spec& spec, const FastDev& f, uint8_t* pt, uint8_t* st, LutOcc* tt,
+                          const uint32_t* magic) {
+  auto clamp = [](int32_t v) { return v < 0 ? 0 : (v > 127 ? 127 : v); };
+  for (int wpb = 0; wpb < kLutW; ++wpb) {
+    FastKernel k{};
+    k.block_size = wpb * 32;   // the largest block of this many warps; thread limits are multiples of 32
+    k.wpb = wpb;
+    k.m_wpb = magic_of(static_cast<uint32_t>(wpb));
+    const int32_t lw = clamp(fast_warps_limit(f, k));
+    for (int u = 0; u < kLutU; ++u) {
+      k.regs = u * 8;          // any count with this many 256-register units per warp
+      k.rpw_units = u;
+      int32_t v = 0;
+      if (wpb != 0) {
+        v = clamp(fast_regs_limit(f, k, k.regs, u, magic_of(static_cast<uint32_t>(u))));
+        v = v < lw ? v : lw;
+        v = v < f.blocks_limit ? v : f.blocks_limit;
+      }
+      pt[wpb * kLutU + u] = static_cast<uint8_t>(v);
+    }
+  }
+  for (int s = 0; s < kLutS; ++s) {
+    FastKernel k{};
+    k.smem = s * 128;          // the largest request of this 128-byte step
+    st[s] = s == kLutS - 1 ? 0 : static_cast<uint8_t>(clamp(fast_smem_limit(f, k, magic)));
+  }
+  const double l_clk = std::log2(static_cast<double>(spec.base_clock_mhz));
+  for (int occ = 0; occ < kLutOcc; ++occ) {
+    LutOcc e{0u, 0u, 0.0f, 0.0f};
+    if (occ > 0) {
+      const uint64_t wave = static_cast<uint64_t>(spec.num_sms) * occ;   // >= 2
+      int s = 0;
+      while ((uint64_t{1} << s) < wave) ++s;                             // ceil(log2 wave) >= 1
+      e.magic = static_cast<uint32_t>((uint64_t{1} << (31 + s)) / wave + 1);
+      e.shift = static_cast<uint32_t>(s - 1);
+      const double a = std::log2(static_cast<double>(occ)) - l_clk;
+      e.lg_hi = static_cast<float>(a);
+      e.lg_lo = static_cast<float>(a - static_cast<double>(e.lg_hi));
+    }
+    tt[occ] = e;
+  }
+}
+
+// Indices the kernel forms from a record (shared with the host-side checks).
+HB_HD uint32_t lut_p_index(uint32_t block_size, uint32_t regs) {
+  const uint32_t wpb = (block_size + 31u) >> 5;
+  const uint32_t units = (regs + 7u) >> 3;
+  return (wpb < kLutW - 1 ? wpb : kLutW - 1) * kLutU + (units < kLutU - 1 ? units : kLutU - 1);
+}
+HB_HD uint32_t lut_s_index(uint32_t smem) {
+  const uint32_t capped = smem < (static_cast<uint32_t>(kLutS - 1) << 7) ? smem : (static_cast<uint32_t>(kLutS - 1) << 7);
+  return (capped + 127u) >> 7;
 }

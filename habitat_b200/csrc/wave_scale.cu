@@ -377,17 +377,7 @@ bool vec4_ok(const Ptrs& p, int64_t K, bool need_gamma) {
 // shared-memory reserve a multiple of 128, shared-memory cap below the table's
 // last step.
 // ---------------------------------------------------------------------------
-constexpr int kMaxClasses = 4;
-constexpr int kLutW = 34;      // warps per block 0..32, 33 = more
-constexpr int kLutU = 34;      // register units per warp 0..32, 33 = more than 256 registers
-constexpr int kLutP = kLutW * kLutU;
-constexpr int kLutS = 2048;    // shared memory in 128-byte steps, last entry = above every cap
-constexpr int kLutOcc = 33;    // occupancies 0..32
-
-struct alignas(16) LutOcc {
-  uint32_t magic, shift;
-  float lg_hi, lg_lo;
-};
+constexpr int kMaxClasses = 4;   // table sizes, LutOcc and the table builder: occupancy.cuh
 
 __device__ uint8_t g_lut_p[HB_MAX_DEVICES * kLutP];
 __device__ uint8_t g_lut_s[HB_MAX_DEVICES * kLutS];
@@ -522,9 +512,8 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const uint32_t wpb = min((static_cast<uint32_t>(bsv.v[i]) + 31u) >> 5, static_cast<uint32_t>(kLutW - 1));
-      const uint32_t units = min((static_cast<uint32_t>(rgv.v[i]) + 7u) >> 3, static_cast<uint32_t>(kLutU - 1));
-      const uint32_t pidx = HB_IDX(wpb * kLutU + units, kLutP, 1);
-      const uint32_t steps = HB_IDX((min(smv.v[i], static_cast<uint32_t>(kLutS - 1) << 7) + 127u) >> 7, kLutS, 2);
+      const uint32_t pidx = HB_IDX(lut_p_index(bsv.v[i], rgv.v[i]), kLutP, 1);
+      const uint32_t steps = HB_IDX(lut_s_index(smv.v[i]), kLutS, 2);
       if (!EXT) {
         uint32_t pw = 0, sw = 0;
 #pragma unroll
@@ -697,57 +686,6 @@ HostTable g_tab;
 GpuCopy g_gpu[kMaxCudaDevices];
 std::atomic<uint64_t> g_version{0};                       // bumped by every hb_set_devices that changed a row
 std::atomic<uint64_t> g_gpu_version[kMaxCudaDevices];     // table version each GPU has seen
-
-// Whether a row can be tabulated for wave_scale_lut_kernel.
-bool lut_row_ok(const hb_device_spec& s, const hb_dev_pre& pre) {
-  return fast_row_ok(s, pre) && s.num_sms >= 2 && pre.max_threads_per_block % 32 == 0 &&
-         pre.max_threads_per_block <= 1024 && pre.smem_reserved % 128 == 0 &&
-         pre.smem_cap <= (kLutS - 2) * 128 && pre.blocks_limit <= kLutOcc - 1 && s.base_clock_mhz > 0;
-}
-
-// Tabulates one device row (host side of hb_set_devices).
-void build_row_lut(const hb_device_spec& spec, const FastDev& f, uint8_t* pt, uint8_t* st, LutOcc* tt,
-                   const uint32_t* magic) {
-  auto clamp = [](int32_t v) { return v < 0 ? 0 : (v > 127 ? 127 : v); };
-  for (int wpb = 0; wpb < kLutW; ++wpb) {
-    FastKernel k{};
-    k.block_size = wpb * 32;   // the largest block of this many warps; thread limits are multiples of 32
-    k.wpb = wpb;
-    k.m_wpb = magic_of(static_cast<uint32_t>(wpb));
-    const int32_t lw = clamp(fast_warps_limit(f, k));
-    for (int u = 0; u < kLutU; ++u) {
-      k.regs = u * 8;          // any count with this many 256-register units per warp
-      k.rpw_units = u;
-      int32_t v = 0;
-      if (wpb != 0) {
-        v = clamp(fast_regs_limit(f, k, k.regs, u, magic_of(static_cast<uint32_t>(u))));
-        v = v < lw ? v : lw;
-        v = v < f.blocks_limit ? v : f.blocks_limit;
-      }
-      pt[wpb * kLutU + u] = static_cast<uint8_t>(v);
-    }
-  }
-  for (int s = 0; s < kLutS; ++s) {
-    FastKernel k{};
-    k.smem = s * 128;          // the largest request of this 128-byte step
-    st[s] = s == kLutS - 1 ? 0 : static_cast<uint8_t>(clamp(fast_smem_limit(f, k, magic)));
-  }
-  const double l_clk = std::log2(static_cast<double>(spec.base_clock_mhz));
-  for (int occ = 0; occ < kLutOcc; ++occ) {
-    LutOcc e{0u, 0u, 0.0f, 0.0f};
-    if (occ > 0) {
-      const uint64_t wave = static_cast<uint64_t>(spec.num_sms) * occ;   // >= 2
-      int s = 0;
-      while ((uint64_t{1} << s) < wave) ++s;                             // ceil(log2 wave) >= 1
-      e.magic = static_cast<uint32_t>((uint64_t{1} << (31 + s)) / wave + 1);
-      e.shift = static_cast<uint32_t>(s - 1);
-      const double a = std::log2(static_cast<double>(occ)) - l_clk;
-      e.lg_hi = static_cast<float>(a);
-      e.lg_lo = static_cast<float>(a - static_cast<double>(e.lg_hi));
-    }
-    tt[occ] = e;
-  }
-}
 
 // Brings the current GPU's copy of the table up to date (rows that changed since its last
 // upload, plus the row-independent tables on first use).  Synchronises the device when it

@@ -49,3 +49,75 @@ extern "C" long harness_magic_errors(void) {
   }
   return bad;
 }
+
+
+// The table kernel's occupancy and wave-count arithmetic, evaluated on the host from the
+// tables the library builds for a device row: occ = min(P[index], S[index]) and
+// floor(nb / (SMs * occ)) = umulhi(nb, M) >> shift.  Returns 0 when the row cannot be tabulated.
+extern "C" int harness_lut(const hb_device_spec* spec, long n, const int* block, const unsigned* smem,
+                           const int* regs, const int* num_blocks, int* occ, unsigned* waves) {
+  const hb_dev_pre pre = hb_fold_device(*spec);
+  if (!lut_row_ok(*spec, pre)) return 0;
+  static uint32_t magic[kMagicN];
+  for (int i = 0; i < kMagicN; ++i) magic[i] = magic_of(static_cast<uint32_t>(i));
+  static uint8_t pt[kLutP], st[kLutS];
+  static LutOcc tt[kLutOcc];
+  build_row_lut(*spec, fold_fast(*spec, pre), pt, st, tt, magic);
+  for (long i = 0; i < n; ++i) {
+    const uint32_t bs = static_cast<uint32_t>(block[i]) & 0xFFFFu, rg = static_cast<uint32_t>(regs[i]) & 0xFFFFu;
+    const uint32_t p = pt[lut_p_index(bs, rg)], s = st[lut_s_index(smem[i])];
+    const uint32_t o = p < s ? p : s;
+    occ[i] = static_cast<int>(o);
+    const LutOcc& e = tt[o];
+    waves[i] = o ? (hb_umulhi(static_cast<uint32_t>(num_blocks[i]), e.magic) >> e.shift) : 0xFFFFFFFFu;
+  }
+  return 1;
+}
+
+#if defined(HARNESS_MAIN)
+// Stand-alone self-check for sanitizer builds: fuzzed device rows and records through every
+// code path above; any out-of-bounds table access or undefined arithmetic aborts the run.
+#include <cstdio>
+#include <random>
+#include <vector>
+int main() {
+  std::mt19937 g(12345);
+  auto pick = [&](std::initializer_list<int> v) { return *(v.begin() + g() % v.size()); };
+  long checked = 0, mismatched = 0;
+  for (int row = 0; row < 400; ++row) {
+    hb_device_spec s{};
+    s.compute_major = pick({3, 5, 6, 7, 8, 9, 10, 12});
+    s.compute_minor = pick({0, 1, 2, 5, 6, 7, 9});
+    s.max_threads_per_block = pick({512, 768, 1000, 1024});
+    s.max_threads_per_multiprocessor = pick({1024, 1536, 2048});
+    s.regs_per_block = pick({32768, 65536});
+    s.regs_per_multiprocessor = pick({65536, 131072});
+    s.warp_size = 32;
+    s.shared_mem_per_block = pick({48 * 1024, 99 * 1024, 163 * 1024, 227 * 1024});
+    s.shared_mem_per_multiprocessor = pick({64 * 1024, 96 * 1024, 100 * 1024, 164 * 1024, 228 * 1024});
+    s.num_sms = 1 + static_cast<int>(g() % 300);
+    s.reserved_shared_mem_per_block = s.compute_major >= 8 ? pick({0, 1024}) : 0;
+    s.mem_bandwidth_gb = 900; s.base_clock_mhz = 1 + static_cast<int>(g() % 3000); s.peak_gflops_per_second = 15000;
+    const int n = 2000;
+    std::vector<int> block(n), regs(n), nb(n), occ(n), ref(n), lim(4 * n);
+    std::vector<unsigned> smem(n), waves(n);
+    std::vector<int> smem_i(n);
+    for (int i = 0; i < n; ++i) {
+      block[i] = static_cast<int>(g() % 1200);
+      regs[i] = static_cast<int>(g() % 300);
+      smem[i] = g() % 4 == 0 ? g() : g() % (240 * 1024);
+      smem_i[i] = smem[i] > 0x7FFF0000u ? -1 : static_cast<int>(smem[i]);
+      nb[i] = static_cast<int>(g() % 0x7FFFFFFFu) + 1;
+    }
+    harness_occupancy(&s, n, block.data(), smem_i.data(), regs.data(), ref.data(), lim.data());
+    if (!harness_lut(&s, n, block.data(), smem.data(), regs.data(), nb.data(), occ.data(), waves.data())) continue;
+    for (int i = 0; i < n; ++i) {
+      ++checked;
+      if (occ[i] != ref[i]) ++mismatched;
+      if (occ[i] > 0 && waves[i] != static_cast<unsigned>(nb[i]) / (static_cast<unsigned>(s.num_sms) * occ[i])) ++mismatched;
+    }
+  }
+  std::printf("checked %ld mismatched %ld\n", checked, mismatched);
+  return (checked > 100000 && mismatched == 0) ? 0 : 1;
+}
+#endif

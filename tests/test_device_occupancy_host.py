@@ -23,6 +23,7 @@ def harness(tmp_path_factory):
     lib.harness_occupancy.restype = None
     lib.harness_fast_occupancy.restype = None
     lib.harness_magic_errors.restype = ctypes.c_long
+    lib.harness_lut.restype = ctypes.c_int
     return lib
 
 
@@ -98,3 +99,87 @@ def test_fast_path_covers_shipped_rows(harness, device_file):
         p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
         harness.harness_fast_occupancy(ctypes.byref(d), ctypes.c_long(100), p(block), p(smem), p(regs), p(fast))
         assert (fast >= 0).all(), name
+
+
+def _run_lut(harness, spec, block, smem, regs, nb):
+    """Occupancy and wave counts as the table kernel forms them, from the tables built for `spec`."""
+    n = len(block)
+    d = _native.DeviceSpec(*[int(v) for v in spec])
+    occ, waves = np.empty(n, np.int32), np.empty(n, np.uint32)
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    ok = harness.harness_lut(ctypes.byref(d), ctypes.c_long(n), p(block), p(smem), p(regs), p(nb), p(occ), p(waves))
+    return bool(ok), occ, waves
+
+
+def test_tables_of_every_shipped_row(harness, device_file):
+    """The P / S / T tables the library builds per device row, read the way the table kernel reads
+    them, against the oracle: every warps-per-block and register step, every 128-byte step of shared
+    memory around its edges, and the exact multiply-shift division on grid sizes up to 2^31 - 1."""
+    g = np.random.Generator(np.random.PCG64(31))
+    block = np.concatenate([np.arange(0, 1100), g.integers(0, 1100, 6000), [2048, 65535]]).astype(np.int32)
+    n = len(block)
+    regs = np.concatenate([np.arange(0, 330), g.integers(0, 300, n - 330)]).astype(np.int32)
+    smem = np.concatenate([np.arange(0, 2050) * 128, np.arange(1, 2051) * 128 - 1, np.arange(0, 2050) * 128 + 1,
+                           g.integers(0, 240 * 1024, n - 3 * 2050)])[:n].astype(np.uint32)
+    smem[-4:] = [0xFFFFFFFF, 0x80000000, 0x7FFF0001, 0x7FFF0000]
+    nb = np.concatenate([g.integers(1, 2 ** 31 - 1, n - 6), [1, 2, 2 ** 31 - 1, 2 ** 31 - 2, 2 ** 30, 12345]]).astype(np.int32)
+    tabulated = 0
+    for name, dev in device_file.items():
+        spec = dev.spec_tuple()
+        ok, occ, waves = _run_lut(harness, spec, block, smem, regs, nb)
+        if not ok:
+            continue
+        tabulated += 1
+        for i in range(n):
+            sm = -1 if smem[i] > 0x7FFF0000 else int(smem[i])
+            o, _ = owave.occupancy(spec, block[i], sm, regs[i])
+            assert occ[i] == o, (name, block[i], smem[i], regs[i])
+            if o:
+                assert waves[i] == int(nb[i]) // (dev.num_sms * o), (name, nb[i], o)
+    assert tabulated >= 8
+
+
+def test_tables_of_fuzzed_rows(harness):
+    """Property test: device rows nobody ships (odd SM counts, thread limits, carve-outs, reserves)."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+    g = np.random.Generator(np.random.PCG64(32))
+    n = 600
+    block = g.integers(0, 1200, n).astype(np.int32)
+    regs = g.integers(0, 300, n).astype(np.int32)
+    smem = g.integers(0, 240 * 1024, n).astype(np.uint32)
+    nb = g.integers(1, 2 ** 31 - 1, n).astype(np.int32)
+    seen = {"tabulated": 0}
+
+    @settings(max_examples=60, deadline=None)
+    @given(major=st.sampled_from([3, 5, 6, 7, 8, 9, 10, 12]), minor=st.sampled_from([0, 1, 2, 5, 6, 7, 9]),
+           tpb=st.sampled_from([512, 768, 1024]), tpm=st.sampled_from([1024, 1536, 2048]),
+           rpb=st.sampled_from([32768, 65536]), rpm=st.sampled_from([65536, 131072]),
+           spb=st.sampled_from([48 * 1024, 99 * 1024, 163 * 1024, 227 * 1024]),
+           spm=st.sampled_from([64 * 1024, 96 * 1024, 100 * 1024, 164 * 1024, 228 * 1024]),
+           sms=st.integers(2, 400), reserve=st.sampled_from([0, 1024]), clock=st.integers(100, 3000))
+    def check(major, minor, tpb, tpm, rpb, rpm, spb, spm, sms, reserve, clock):
+        spec = (major, minor, tpb, tpm, rpb, rpm, 32, spb, spm, sms, 0, reserve if major >= 8 else 0, 900, clock, 15000)
+        ok, occ, waves = _run_lut(harness, spec, block, smem, regs, nb)
+        if not ok:
+            return
+        seen["tabulated"] += 1
+        for i in range(0, n, 3):
+            o, _ = owave.occupancy(spec, block[i], int(smem[i]), regs[i])
+            assert occ[i] == o, (spec, block[i], smem[i], regs[i])
+            if o:
+                assert waves[i] == int(nb[i]) // (sms * o)
+    check()
+    assert seen["tabulated"] >= 10
+
+
+def test_host_code_under_sanitizers(tmp_path):
+    """The library's host-compilable integer code and its table builder, built with
+    -fsanitize=address,undefined and driven with fuzzed rows and records (the harness's main):
+    an out-of-range table index or undefined arithmetic aborts the run."""
+    exe = str(tmp_path / "harness_sanitized")
+    subprocess.run(["g++", "-O1", "-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-sanitize-recover=all",
+                    "-DHARNESS_MAIN", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(ROOT, "habitat_b200", "csrc"),
+                    os.path.join(HERE, "occupancy_host_harness.cpp"), "-o", exe], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "mismatched 0" in r.stdout, r.stdout + r.stderr
