@@ -12,8 +12,8 @@ It imports the reference's modules from where they lie (as make_golden.py does) 
     13,108 single-kernel operations (origin V100) to each of the five other rows the
     reference's devices.yml shares with the benchmark's device classes = 65,540 pairs.
 Kernels are rejection-sampled so that the origin can run them (the reference raises
-ZeroDivisionError otherwise).  The figures go into BASELINE.md by hand; the reference
-cannot travel to a GPU box, so this is not part of any test or benchmark.
+ZeroDivisionError otherwise).  The reference cannot travel to a GPU box, so this is not part
+of any test or benchmark; its figures are quoted in the project's notes.
 """
 import json
 import os
