@@ -909,11 +909,36 @@ extern "C" hb_status hb_mlp_create(hb_mlp** handle, int32_t n_op_features, int32
     hb::set_error("hb_mlp_create: NULL argument");
     return HB_ERR_INVALID_ARGUMENT;
   }
-  if (width != kWidth || layers < 1 || layers > 64 || n_op_features < 1 ||
+  if (width < 1 || width > kWidth || layers < 1 || layers > 64 || n_op_features < 1 ||
       n_op_features + 4 > kMaxInFeat || n_device_rows < 1 || n_device_rows > 256 ||
       (precision != HB_PRECISION_BF16 && precision != HB_PRECISION_BF16X3)) {
-    hb::set_error("hb_mlp_create: unsupported shape (width must be 1024, 1 <= F <= 8, layers >= 1)");
+    hb::set_error("hb_mlp_create: unsupported shape (1 <= width <= 1024, 1 <= F <= 8, 1 <= layers <= 64)");
     return HB_ERR_UNSUPPORTED;
+  }
+  // The kernel is built for 1024-wide layers.  A narrower network runs as a 1024-wide one whose
+  // extra features have zero weights and zero bias: they stay 0 through every ReLU and add
+  // nothing to any sum, so the results are those of the narrow network.
+  std::vector<float> pad_fc1_w, pad_fc1_b, pad_hidden_w, pad_hidden_b, pad_fc2_w;
+  if (width < kWidth) {
+    const int C = n_op_features + 4;
+    pad_fc1_w.assign(static_cast<size_t>(kWidth) * C, 0.0f);
+    pad_fc1_b.assign(kWidth, 0.0f);
+    pad_hidden_w.assign(static_cast<size_t>(layers) * kWidth * kWidth, 0.0f);
+    pad_hidden_b.assign(static_cast<size_t>(layers) * kWidth, 0.0f);
+    pad_fc2_w.assign(kWidth, 0.0f);
+    std::memcpy(pad_fc1_w.data(), fc1_w, sizeof(float) * width * C);
+    std::memcpy(pad_fc1_b.data(), fc1_b, sizeof(float) * width);
+    std::memcpy(pad_fc2_w.data(), fc2_w, sizeof(float) * width);
+    for (int L = 0; L < layers; ++L) {
+      std::memcpy(&pad_hidden_b[static_cast<size_t>(L) * kWidth], hidden_b + static_cast<size_t>(L) * width,
+                  sizeof(float) * width);
+      for (int r = 0; r < width; ++r)
+        std::memcpy(&pad_hidden_w[(static_cast<size_t>(L) * kWidth + r) * kWidth],
+                    hidden_w + (static_cast<size_t>(L) * width + r) * width, sizeof(float) * width);
+    }
+    fc1_w = pad_fc1_w.data(); fc1_b = pad_fc1_b.data();
+    hidden_w = pad_hidden_w.data(); hidden_b = pad_hidden_b.data();
+    fc2_w = pad_fc2_w.data();
   }
   const bool split = precision == HB_PRECISION_BF16X3;
   const int C_in = n_op_features + 4;

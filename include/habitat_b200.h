@@ -208,7 +208,9 @@ enum { HB_PRECISION_BF16 = 0, HB_PRECISION_BF16X3 = 1 };
  *   hidden_b [layers][width], fc2_w [width], fc2_b [1], mu/sigma [F+4].
  * device_features is [n_device_rows][4] = (mem, mem_bw, num_sm, single), the
  * columns RuntimePredictor.predict reads from devices.csv
- * (analysis/mlp/devices.py:5-10, mlp.py:125).  width must be 1024. */
+ * (analysis/mlp/devices.py:5-10, mlp.py:125).  1 <= width <= 1024 (the shipped
+ * predictors are 1024 wide; a narrower network is zero-padded to 1024 inside the
+ * pack and costs as much), 1 <= layers <= 64. */
 hb_status hb_mlp_create(hb_mlp** handle, int32_t n_op_features, int32_t layers, int32_t width,
                         const float* fc1_w, const float* fc1_b, const float* hidden_w,
                         const float* hidden_b, const float* fc2_w, const float* fc2_b,

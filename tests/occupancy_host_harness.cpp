@@ -74,6 +74,30 @@ extern "C" int harness_lut(const hb_device_spec* spec, long n, const int* block,
   return 1;
 }
 
+// The three tables of a device row as the library builds them: P [34 * 34] bytes, S [2048] bytes,
+// T [33][4] 32-bit words {multiplier, shift, A_hi bits, A_lo bits}.  Returns 0 when the row cannot
+// be tabulated.
+extern "C" int harness_tables(const hb_device_spec* spec, unsigned char* p_out, unsigned char* s_out,
+                              unsigned* t_out) {
+  const hb_dev_pre pre = hb_fold_device(*spec);
+  if (!lut_row_ok(*spec, pre)) return 0;
+  uint32_t magic[kMagicN];
+  for (int i = 0; i < kMagicN; ++i) magic[i] = magic_of(static_cast<uint32_t>(i));
+  LutOcc tt[kLutOcc];
+  build_row_lut(*spec, fold_fast(*spec, pre), p_out, s_out, tt, magic);
+  static_assert(sizeof(LutOcc) == 16, "four 32-bit words per entry");
+  for (int i = 0; i < kLutOcc; ++i) {
+    t_out[4 * i] = tt[i].magic;
+    t_out[4 * i + 1] = tt[i].shift;
+    float f[2] = {tt[i].lg_hi, tt[i].lg_lo};
+    unsigned u[2];
+    __builtin_memcpy(u, f, 8);
+    t_out[4 * i + 2] = u[0];
+    t_out[4 * i + 3] = u[1];
+  }
+  return 1;
+}
+
 #if defined(HARNESS_MAIN)
 // Stand-alone self-check for sanitizer builds: fuzzed device rows and records through every
 // code path above; any out-of-bounds table access or undefined arithmetic aborts the run.

@@ -24,6 +24,7 @@ def harness(tmp_path_factory):
     lib.harness_fast_occupancy.restype = None
     lib.harness_magic_errors.restype = ctypes.c_long
     lib.harness_lut.restype = ctypes.c_int
+    lib.harness_tables.restype = ctypes.c_int
     return lib
 
 
@@ -183,3 +184,69 @@ def test_host_code_under_sanitizers(tmp_path):
                     os.path.join(HERE, "occupancy_host_harness.cpp"), "-o", exe], check=True)
     r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "mismatched 0" in r.stdout, r.stdout + r.stderr
+
+
+def test_table_kernel_arithmetic_in_float32(harness, bench_devices):
+    """The float32 formulation of the table kernel, replayed in numpy from the library's own
+    tables, against the float64 oracle: wave counts by multiply-shift, the small-kernel exponent
+    (1 - gamma) (A_dest[m_d] - A_origin[m_o]) from hi + lo table entries, the large-kernel exponent
+    from split constants, one exp2 per pair.  Guards the 1e-6 error budget without a GPU (the
+    device adds the error of ex2.approx, two units in the last place)."""
+    from habitat_b200 import workloads
+    K = 1 << 16
+    k = workloads.make_kernels(K, 1002)
+    specs = [d.spec_tuple() for d in bench_devices]
+    ref = owave.wave_scale_batch(specs, 0, list(range(6)), k, want_limits=False)
+
+    def tables(spec):
+        d = _native.DeviceSpec(*[int(v) for v in spec])
+        P, S, T = np.empty(34 * 34, np.uint8), np.empty(2048, np.uint8), np.empty(33 * 4, np.uint32)
+        p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        assert harness.harness_tables(ctypes.byref(d), p(P), p(S), p(T))
+        T = T.reshape(33, 4)
+        return P, S, T[:, 0].astype(np.uint64), T[:, 1].astype(np.uint64), T[:, 2].copy().view(np.float32), \
+            T[:, 3].copy().view(np.float32)
+
+    f32 = np.float32
+    bs, rg, sm = k["block_size"].astype(np.uint32), k["regs_per_thread"].astype(np.uint32), k["smem_bytes"].astype(np.uint32)
+    pidx = np.minimum((bs + 31) >> 5, 33) * 34 + np.minimum((rg + 7) >> 3, 33)
+    sidx = (np.minimum(sm, 2047 << 7) + 127) >> 7
+    nb = k["num_blocks"].astype(np.uint64)
+    t, g = k["run_time_ns"].astype(f32), k["gamma"].astype(f32)
+    omg = (f32(1.0) - g).astype(f32)
+    tab = [tables(s) for s in specs]
+    origin = bench_devices[0]
+
+    def occ_waves(i):
+        P, S, M, sh, _, _ = tab[i]
+        occ = np.minimum(P[pidx], S[sidx]).astype(np.int64)
+        q = ((nb * M[occ]) >> np.uint64(32)) >> sh[occ]
+        return occ, q
+
+    occ_o, q_o = occ_waves(0)
+    assert np.array_equal(occ_o, ref["origin_occupancy"])
+    live = occ_o > 0
+    fits_o = live & (q_o == 0)
+    om = np.where(fits_o, -(-nb.astype(np.int64) // origin.num_sms), 1)
+    ao_hi, ao_lo = tab[0][4][om], tab[0][5][om]
+    worst = 0.0
+    for d, dev in enumerate(bench_devices):
+        occ, q = occ_waves(d)
+        assert np.array_equal(occ, ref["dest_occupancy"][d])
+        has = occ > 0
+        assert np.array_equal(np.where(has, q, 0xFFFFFFFF).astype(np.uint32), ref["dest_waves"][d])
+        small = fits_o & has & (q == 0)
+        ok = live & ~(fits_o & ~has)
+        assert np.array_equal(ok, ref["status"][d] <= 1) and np.array_equal(small, ref["status"][d] == 1)
+        dm = np.where(small, -(-nb.astype(np.int64) // dev.num_sms), 1)
+        e_small = (omg * ((tab[d][4][dm] - ao_hi).astype(f32) + (tab[d][5][dm] - ao_lo).astype(f32)).astype(f32)).astype(f32)
+        b = np.log2(origin.base_clock_mhz / dev.base_clock_mhz) + np.log2(origin.num_sms / dev.num_sms)
+        a = np.log2(origin.mem_bandwidth_gb / dev.mem_bandwidth_gb) - b
+        a_hi, b_hi = f32(a), f32(b)
+        a_lo, b_lo = f32(a - np.float64(a_hi)), f32(b - np.float64(b_hi))
+        fma = lambda x, y, z: (x.astype(np.float64) * np.float64(y) + np.float64(z)).astype(f32)
+        e = np.where(small, e_small, (fma(g, a_hi, b_hi) + fma(g, a_lo, b_lo)).astype(f32))
+        out = (t * np.exp2(e.astype(np.float64)).astype(f32)).astype(f32)
+        err = np.abs(out[ok].astype(np.float64) - ref["scaled_ns"][d][ok]) / ref["scaled_ns"][d][ok]
+        worst = max(worst, float(err.max()))
+    assert worst <= 5e-7, worst          # leaves room for the device's approximate exp2 inside 1e-6

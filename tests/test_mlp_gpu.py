@@ -190,3 +190,23 @@ def test_timeout_status_is_reported_once():
     h.check_status()
     assert np.array_equal(first, again)
     h.close()
+
+
+@pytest.mark.parametrize("width,layers", [(256, 3), (1000, 2), (64, 1)])
+def test_other_layer_sizes(width, layers):
+    """RuntimePredictor(model_name, layers, layer_size) takes any size in the reference
+    (analysis/mlp/mlp.py:113-131); widths up to 1024 run zero-padded on the 1024-wide kernel."""
+    op = "lstm"
+    w = workloads.init_mlp_weights(op, seed=width + layers, layers=layers, width=width, gain=np.sqrt(6.0))
+    for precision, tol in (("bf16", 4e-2), ("bf16x3", 1e-4)):
+        got, ref32, ref64 = _run(op, 700, w, precision, seed=width)
+        spread = np.abs(ref64).max()
+        assert np.abs(got - ref64).max() <= tol * spread, (precision, np.abs(got - ref64).max() / spread)
+    with pytest.raises(_native_error()):
+        wide = workloads.init_mlp_weights(op, seed=1, layers=1, width=1088)
+        _run(op, 10, wide, "bf16", seed=1)
+
+
+def _native_error():
+    from habitat_b200 import _native
+    return _native.HabitatNativeError
