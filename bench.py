@@ -1106,10 +1106,13 @@ def main():
         line["gpu_launches"] = timed_launches
         line["gpu_launches_whole_run"] = ctx.launches
         if not args.skip_cpu:
-            line["cpu_baseline"] = cpu_wave()
-            line["cpu_baseline"].pop("seconds"), line["cpu_baseline"].pop("pairs")
-            mlp["cpu_baseline"] = cpu_mlp()
-            mlp["cpu_baseline"].pop("seconds"), mlp["cpu_baseline"].pop("queries")
+            if world == 1:
+                # the timed CPU baseline belongs to the single-GPU run (the box's host cores are the
+                # same at every N); the oracle checks below run at every N
+                line["cpu_baseline"] = cpu_wave()
+                line["cpu_baseline"].pop("seconds"), line["cpu_baseline"].pop("pairs")
+                mlp["cpu_baseline"] = cpu_mlp()
+                mlp["cpu_baseline"].pop("seconds"), mlp["cpu_baseline"].pop("queries")
             check["oracle_subset"] = oracle_subset_check(ctx, sw)
         line["mlp"] = mlp
         line["multi_gpu_check"] = check

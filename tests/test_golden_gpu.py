@@ -153,6 +153,9 @@ def test_trace_to_device(device_file, tmp_path):
         assert pt.device is dest and len(pt.operations) == len(trace.operations)
         with pytest.raises(RuntimeError):
             pt.operations[0].to_device(origin, predictor)
+    # metrics, the register table and the raise-on-NaN rule all ride on the tabulated kernel
+    from habitat_b200 import batched
+    assert batched.wave_scale_path() == "wave_scale_lut_kernel"
     many = trace.to_devices(dests, predictor)             # all destinations in one pass
     for d, pt in enumerate(many):
         assert abs(pt.run_time_ms - g["total_ms"][d]) <= 2e-2 * g["total_ms"][d]
