@@ -260,6 +260,7 @@ class Ctx:
             ok = 1.0
             try:
                 self.peer = hd.PeerTotals()
+                self.peer.set_wait(4.0)      # a rank may stall for a moment (host jitter) without failing the run
             except Exception as exc:                       # noqa: BLE001 - any failure means NCCL
                 print("peer exchange unavailable on rank %d: %s" % (self.rank, exc), file=sys.stderr)
                 ok = 0.0
@@ -976,23 +977,46 @@ def main():
             ctx.dist.all_reduce(flag, op=ctx.dist.ReduceOp.MAX)
             if float(flag.item()) != 0.0:
                 ctx.totals_via = "nccl"                    # every rank falls back together
-        ctx.barrier()
-        sampler.mark("timed_start")
-        t0, t1 = ctx.event(), ctx.event()
-        launches_before = ctx.launches
-        t0.record(ctx.stream)
-        for i in range(steps):
-            sw.step(warm + i)
-        t1.record(ctx.stream)
-        ctx.barrier()
-        sampler.mark("timed_end")
-        timed_launches = ctx.launches - launches_before
-        total_ms = ctx.reduce(t0.elapsed_time(t1))
+        def timed_region():
+            sw.ev.clear()
+            ctx.barrier()
+            sampler.mark("timed_start")
+            t0, t1 = ctx.event(), ctx.event()
+            before = ctx.launches
+            t0.record(ctx.stream)
+            for i in range(steps):
+                sw.step(warm + i)
+            t1.record(ctx.stream)
+            ctx.barrier()
+            sampler.mark("timed_end")
+            return ctx.launches - before, t0.elapsed_time(t1)
+
+        timed_launches, total_ms = timed_region()
+        tot_host = sw.totals.cpu().numpy()
+        fallback_reason = None
+        if ctx.totals_via == "peer":
+            # a wait for a peer that ran out (NaN totals, status word set) on any rank: every rank
+            # repeats the timed region with NCCL all-reduces
+            bad = 0.0
+            try:
+                ctx.peer.check_status()
+                if not np.isfinite(tot_host[warm:]).all():
+                    bad = 1.0
+            except Exception as exc:                       # noqa: BLE001
+                print("peer exchange failed in the timed steps on rank %d: %s" % (rank, exc), file=sys.stderr)
+                bad = 1.0
+            flag = torch.tensor([bad], device="cuda")
+            ctx.dist.all_reduce(flag, op=ctx.dist.ReduceOp.MAX)
+            if float(flag.item()) != 0.0:
+                fallback_reason = "a wait of the peer exchange ran out during the timed steps; they were repeated with NCCL"
+                ctx.totals_via = "nccl"
+                timed_launches, total_ms = timed_region()
+                tot_host = sw.totals.cpu().numpy()
+        total_ms = ctx.reduce(total_ms)
         w_ms, k_ms, m_ms, per_op_ms = sw.phase_ms()
         w_ms, m_ms = ctx.reduce(w_ms), ctx.reduce(m_ms)
         for h in sw.handles.values():
             h.check_status()
-        tot_host = sw.totals.cpu().numpy()
         same_every_step = bool((tot_host[warm:] == tot_host[warm]).all())
 
         shard_pairs = (sw.khi - sw.klo) * WAVE_D
@@ -1025,7 +1049,7 @@ def main():
                                    "GPUs' memory and adds up what the peers stored (five exchanges per step: [6] pair "
                                    "totals, 4 x [6] query totals), checked against NCCL all-reduces in the warm-up"
                            }[ctx.totals_via],
-            "peer_vs_nccl_max_rel_diff": exchange_check,
+            "peer_vs_nccl_max_rel_diff": exchange_check, "collective_fallback": fallback_reason,
             "wave_phase_ms_per_step": w_ms / steps, "mlp_phase_ms_per_step": m_ms / steps,
             "e2e": "the rank's shard from pinned host memory through the host pipelines: one 20 B/kernel block up "
                    "and the predicted times (4 B/pair) down per 1,048,576-kernel chunk; features up (4 F + 1 B per "
