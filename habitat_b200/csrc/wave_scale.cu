@@ -571,8 +571,10 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
       live[i] = nbok[i] && occ != 0u;
       owav.v[i] = live[i] ? q : 0xFFFFFFFFu;
       fits_o[i] = live[i] && q == 0u;            // num_blocks < origin wave size
-      // ceil(num_blocks / SMs) <= occupancy <= 32 whenever the small-kernel rule applies
-      const uint32_t om = fits_o[i] ? __umulhi(static_cast<uint32_t>(nb) + og.sm.x, og.sm.y) : 1u;
+      // ceil(num_blocks / SMs) <= occupancy <= 32 whenever the small-kernel rule applies; otherwise
+      // the entry read here is never used, and the clamp only keeps the index inside the table.  Not
+      // selecting on fits_o keeps this load independent of the one above.
+      const uint32_t om = min(__umulhi(static_cast<uint32_t>(nb) + og.sm.x, og.sm.y), static_cast<uint32_t>(kLutOcc - 1));
       lg_o[i] = __ldg(reinterpret_cast<const float2*>(tab_t + (og.sel.z + HB_IDX(om, kLutOcc, 4) * 16u + 8u)));
     }
     store_byte_pair<VEC, ALIGNED>(p.origin_occ + k0, o2, pair);
@@ -624,7 +626,9 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
         // kernel fits in one origin wave
         const bool small = fits_o[i] && has_wave && q == 0u;
         const bool ok = live[i] && !(fits_o[i] && !has_wave);
-        const uint32_t dm = small ? __umulhi(static_cast<uint32_t>(nb) + dd.sm.x, dd.sm.y) : 1u;
+        // blocks per SM on the destination: meaningful (and <= occupancy) when `small`; computed from
+        // the record alone so that this table load does not wait for the one above
+        const uint32_t dm = min(__umulhi(static_cast<uint32_t>(nb) + dd.sm.x, dd.sm.y), static_cast<uint32_t>(kLutOcc - 1));
         const float2 lg_d = __ldg(reinterpret_cast<const float2*>(tab_t + (dd.sel.z + HB_IDX(dm, kLutOcc, 7) * 16u + 8u)));
         float gamma, one_minus;
         if (with_metrics) {
