@@ -192,7 +192,7 @@ def run_reference(args):
     if rank != 0:
         return
     steps = max(1, args.steps)
-    per = max(0.5, min(6.0, 60.0 / (steps + args.warmup)))
+    per = args.cpu_seconds if args.cpu_seconds > 0 else max(0.5, min(6.0, 60.0 / (steps + args.warmup)))
     wave = cpu_wave(target_s=per, repeats=steps + args.warmup)
     timed = wave.pop("seconds")[args.warmup:]
     wave_s = float(np.sum(timed))
@@ -918,6 +918,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg and the oracle checks")
+    ap.add_argument("--cpu-seconds", type=float, default=0.0,
+                    help="reference arm: seconds of CPU work per step and phase (default: sized to the step count)")
     ap.add_argument("--totals", default="peer", choices=["peer", "nccl"],
                     help="how the per-step totals are summed across GPUs")
     ap.add_argument("--case", default="all",
