@@ -680,7 +680,7 @@ struct HostTable {
   std::vector<LutOcc> lut_t = std::vector<LutOcc>(static_cast<size_t>(HB_MAX_DEVICES) * kLutOcc);
 };
 struct GpuCopy {
-  bool constants = false;                      // row-independent tables uploaded
+  std::atomic<bool> constants{false};          // row-independent tables uploaded (read without the lock)
   uint64_t row_version[HB_MAX_DEVICES] = {};   // version of each row this GPU holds
   int sm_count = 0;
 };
@@ -702,14 +702,14 @@ hb_status sync_gpu(int* sm_count) {
     return HB_ERR_UNSUPPORTED;
   }
   if (g_gpu_version[dev].load(std::memory_order_acquire) == g_version.load(std::memory_order_acquire) &&
-      g_gpu[dev].constants) {
+      g_gpu[dev].constants.load(std::memory_order_acquire)) {
     if (sm_count) *sm_count = g_gpu[dev].sm_count;
     return HB_OK;
   }
   std::lock_guard<std::mutex> lock(g_mu);
   GpuCopy& gc = g_gpu[dev];
   bool uploaded = false;
-  if (!gc.constants) {
+  if (!gc.constants.load(std::memory_order_relaxed)) {
     HB_CUDA_TRY(cudaDeviceGetAttribute(&gc.sm_count, cudaDevAttrMultiProcessorCount, dev));
     double lg[65];
     lg[0] = 0.0;
@@ -718,7 +718,7 @@ hb_status sync_gpu(int* sm_count) {
     uint32_t magic[kMagicN];
     for (int i = 0; i < kMagicN; ++i) magic[i] = magic_of(static_cast<uint32_t>(i));
     HB_CUDA_TRY(cudaMemcpyToSymbol(g_magic, magic, sizeof(magic)));
-    gc.constants = true;
+    gc.constants.store(true, std::memory_order_release);
     uploaded = true;
   }
   for (int i = 0; i < g_tab.n; ++i) {
