@@ -20,7 +20,7 @@
 // calls of a handle to be ordered on each GPU (one stream, or events), and every rank to make
 // the same calls in the same order.
 //
-// Every wait is bounded (kPeerWaitNs): when it runs out the kernel records which (rank, slot)
+// Every wait is bounded (one second unless hb_peer_set_wait_ns says otherwise): when it runs out the kernel records which (rank, slot)
 // it gave up on in the handle's status word, writes NaN and returns; nothing traps.  No
 // multicast of any kind is used: stores go to each peer in turn.
 #include <cuda_runtime.h>
@@ -31,15 +31,12 @@
 #include <vector>
 
 #include "hb_common.h"
+#include "reduce_stage1.cuh"
 
 namespace {
 
 constexpr int kPeerSlots = 64;            // values per call
 constexpr int kPeerMaxWorld = 16;
-constexpr int kSumThreads = 256;
-constexpr int kPlaneBlocks = 256;
-constexpr int kGroupBlocks = 256;
-constexpr int kMaxGroups = 8;
 
 struct PeerSlot {
   double value;
@@ -107,67 +104,6 @@ __device__ __forceinline__ double peer_collect(const PeerView& pv, int i, double
     for (int q = 0; q < pv.world; ++q) total += sh[q];
   __syncthreads();
   return total;
-}
-
-__device__ __forceinline__ double warp_sum(double v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xFFFFFFFFu, v, o);
-  return v;
-}
-__device__ __forceinline__ double block_sum(double v) {
-  __shared__ double s[kSumThreads / 32];
-  v = warp_sum(v);
-  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
-  __syncthreads();
-  double t = 0.0;
-  if (threadIdx.x < 32) {
-    t = threadIdx.x < kSumThreads / 32 ? s[threadIdx.x] : 0.0;
-    t = warp_sum(t);
-  }
-  __syncthreads();
-  return t;
-}
-
-// Stage 1 kernels: as in reduce.cu (fixed chunks, float64, NaN skipped).
-__global__ void __launch_bounds__(kSumThreads)
-peer_plane_partial_kernel(const float* __restrict__ values, int64_t plane_len, double* __restrict__ partial) {
-  hb_grid_dependency_wait();
-  const int plane = blockIdx.y;
-  const float* v = values + static_cast<int64_t>(plane) * plane_len;
-  const int64_t chunk = (plane_len + kPlaneBlocks - 1) / kPlaneBlocks;
-  const int64_t lo = static_cast<int64_t>(blockIdx.x) * chunk;
-  const int64_t hi = lo + chunk < plane_len ? lo + chunk : plane_len;
-  double acc = 0.0;
-  for (int64_t i = lo + threadIdx.x; i < hi; i += kSumThreads) {
-    const float x = v[i];
-    if (x == x) acc += static_cast<double>(x);
-  }
-  const double t = block_sum(acc);
-  if (threadIdx.x == 0) partial[plane * kPlaneBlocks + blockIdx.x] = t;
-}
-
-__global__ void __launch_bounds__(kSumThreads)
-peer_group_partial_kernel(const float* __restrict__ values, const uint8_t* __restrict__ keys, int64_t n,
-                          int32_t n_groups, double* __restrict__ partial) {
-  hb_grid_dependency_wait();
-  const int64_t chunk = (n + kGroupBlocks - 1) / kGroupBlocks;
-  const int64_t lo = static_cast<int64_t>(blockIdx.x) * chunk;
-  const int64_t hi = lo + chunk < n ? lo + chunk : n;
-  double acc[kMaxGroups];
-#pragma unroll
-  for (int g = 0; g < kMaxGroups; ++g) acc[g] = 0.0;
-  for (int64_t i = lo + threadIdx.x; i < hi; i += kSumThreads) {
-    const float x = values[i];
-    const int key = keys[i];
-    const double v = x == x ? static_cast<double>(x) : 0.0;
-#pragma unroll
-    for (int g = 0; g < kMaxGroups; ++g) acc[g] += key == g ? v : 0.0;
-  }
-#pragma unroll
-  for (int g = 0; g < kMaxGroups; ++g) {
-    const double t = block_sum(acc[g]);
-    if (threadIdx.x == 0 && g < n_groups) partial[g * kGroupBlocks + blockIdx.x] = t;
-  }
 }
 
 // Final stage + exchange: block i adds the 256 partial sums of value i, publishes the result
@@ -368,7 +304,7 @@ extern "C" hb_status hb_plane_sum_allreduce(hb_peer* h, const float* values, int
   if (st != HB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   ++h->seq;
-  HB_CUDA_TRY(hb::launch_overlapped(peer_plane_partial_kernel, dim3(kPlaneBlocks, n_planes), dim3(kSumThreads), 0, s,
+  HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(kPlaneBlocks, n_planes), dim3(kSumThreads), 0, s,
                                     values, plane_len, h->partial));
   HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n_planes), dim3(kSumThreads), 0, s,
                                     static_cast<const double*>(h->partial), out, view_of(h), 3));
@@ -385,8 +321,8 @@ extern "C" hb_status hb_group_sum_allreduce(hb_peer* h, const float* values, con
   if (st != HB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   ++h->seq;
-  HB_CUDA_TRY(hb::launch_overlapped(peer_group_partial_kernel, dim3(kGroupBlocks), dim3(kSumThreads), 0, s, values,
-                                    keys, n, n_groups, h->partial));
+  HB_CUDA_TRY(hb::launch_overlapped(group_partial_kernel, dim3(kGroupBlocks), dim3(kSumThreads), 0, s, values,
+                                    keys, n, 0, n_groups, h->partial));
   HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n_groups), dim3(kSumThreads), 0, s,
                                     static_cast<const double*>(h->partial), out, view_of(h), 3));
   return HB_OK;

@@ -13,31 +13,9 @@
 #include <mutex>
 
 #include "hb_common.h"
+#include "reduce_stage1.cuh"
 
 namespace {
-
-constexpr int kSumThreads = 256;
-
-__device__ __forceinline__ double warp_sum(double v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xFFFFFFFFu, v, o);
-  return v;
-}
-
-// Block-wide sum of one value per thread; valid in thread 0.
-__device__ __forceinline__ double block_sum(double v) {
-  __shared__ double s[kSumThreads / 32];
-  v = warp_sum(v);
-  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
-  __syncthreads();
-  double t = 0.0;
-  if (threadIdx.x < 32) {
-    t = threadIdx.x < kSumThreads / 32 ? s[threadIdx.x] : 0.0;
-    t = warp_sum(t);
-  }
-  __syncthreads();
-  return t;
-}
 
 // One block per segment.
 __global__ void __launch_bounds__(kSumThreads)
@@ -50,28 +28,6 @@ segment_sum_kernel(const float* __restrict__ values, const int64_t* __restrict__
     const double t = block_sum(acc);
     if (threadIdx.x == 0) out[s] = t;
   }
-}
-
-// Stage 1 of the plane sum: a fixed number of blocks per plane, each summing a
-// fixed contiguous chunk; NaN entries (pairs the reference raises on) skipped.
-constexpr int kPlaneBlocks = 256;
-
-__global__ void __launch_bounds__(kSumThreads)
-plane_partial_kernel(const float* __restrict__ values, int64_t plane_len,
-                     double* __restrict__ partial) {
-  hb_grid_dependency_wait();
-  const int plane = blockIdx.y;
-  const float* v = values + static_cast<int64_t>(plane) * plane_len;
-  const int64_t chunk = (plane_len + kPlaneBlocks - 1) / kPlaneBlocks;
-  const int64_t lo = static_cast<int64_t>(blockIdx.x) * chunk;
-  const int64_t hi = lo + chunk < plane_len ? lo + chunk : plane_len;
-  double acc = 0.0;
-  for (int64_t i = lo + threadIdx.x; i < hi; i += kSumThreads) {
-    const float x = v[i];
-    if (x == x) acc += static_cast<double>(x);
-  }
-  const double t = block_sum(acc);
-  if (threadIdx.x == 0) partial[plane * kPlaneBlocks + blockIdx.x] = t;
 }
 
 __global__ void __launch_bounds__(kSumThreads)
@@ -101,36 +57,6 @@ special_scale_kernel(const float* __restrict__ run_time_ms, const float* __restr
   if (negative_count) {
     const unsigned m = __ballot_sync(0xFFFFFFFFu, neg);
     if ((threadIdx.x & 31) == 0 && m) atomicAdd(negative_count, __popc(m));
-  }
-}
-
-// Stage 1 of the group sum: values carry a small group key each (the device row of an MLP
-// query); a block sums a fixed contiguous chunk into one accumulator per group.  Keys at or
-// above n_groups and NaN values are skipped.
-constexpr int kGroupBlocks = 256;
-constexpr int kMaxGroups = 8;     // groups per pass; more groups take more passes
-
-__global__ void __launch_bounds__(kSumThreads)
-group_partial_kernel(const float* __restrict__ values, const uint8_t* __restrict__ keys, int64_t n,
-                     int32_t group0, int32_t n_groups, double* __restrict__ partial) {
-  hb_grid_dependency_wait();
-  const int64_t chunk = (n + kGroupBlocks - 1) / kGroupBlocks;
-  const int64_t lo = static_cast<int64_t>(blockIdx.x) * chunk;
-  const int64_t hi = lo + chunk < n ? lo + chunk : n;
-  double acc[kMaxGroups];
-#pragma unroll
-  for (int g = 0; g < kMaxGroups; ++g) acc[g] = 0.0;
-  for (int64_t i = lo + threadIdx.x; i < hi; i += kSumThreads) {
-    const float x = values[i];
-    const int key = static_cast<int>(keys[i]) - group0;
-    const double v = x == x ? static_cast<double>(x) : 0.0;
-#pragma unroll
-    for (int g = 0; g < kMaxGroups; ++g) acc[g] += key == g ? v : 0.0;
-  }
-#pragma unroll
-  for (int g = 0; g < kMaxGroups; ++g) {
-    const double t = block_sum(acc[g]);
-    if (threadIdx.x == 0 && g < n_groups) partial[g * kGroupBlocks + blockIdx.x] = t;
   }
 }
 

@@ -1,0 +1,107 @@
+// First stage of the two-stage float64 sums, shared by reduce.cu (local totals) and
+// peer_exchange.cu (totals exchanged between GPUs): a fixed number of blocks, each summing a fixed
+// contiguous chunk with a fixed assignment of elements to lanes and a fixed reduction tree, so the
+// result does not depend on scheduling (no floating-point atomics) and is the same bits in both files.
+#pragma once
+
+#include "hb_common.h"
+
+namespace {
+
+constexpr int kSumThreads = 256;
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+// Block-wide sum of one value per thread; valid in thread 0.
+__device__ __forceinline__ double block_sum(double v) {
+  __shared__ double s[kSumThreads / 32];
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+  __syncthreads();
+  double t = 0.0;
+  if (threadIdx.x < 32) {
+    t = threadIdx.x < kSumThreads / 32 ? s[threadIdx.x] : 0.0;
+    t = warp_sum(t);
+  }
+  __syncthreads();
+  return t;
+}
+
+// Stage 1 of the plane sum: a fixed number of blocks per plane, each summing a
+// fixed contiguous chunk; NaN entries (pairs the reference raises on) skipped.
+constexpr int kPlaneBlocks = 256;
+
+__global__ void __launch_bounds__(kSumThreads)
+plane_partial_kernel(const float* __restrict__ values, int64_t plane_len,
+                     double* __restrict__ partial) {
+  hb_grid_dependency_wait();
+  const int plane = blockIdx.y;
+  const float* v = values + static_cast<int64_t>(plane) * plane_len;
+  const int64_t chunk = (plane_len + kPlaneBlocks - 1) / kPlaneBlocks;
+  const int64_t lo = static_cast<int64_t>(blockIdx.x) * chunk;
+  const int64_t hi = lo + chunk < plane_len ? lo + chunk : plane_len;
+  // The bulk of a chunk goes through 16-byte loads with four independent accumulators (the
+  // assignment of elements to accumulators is fixed, so the result is the same for every launch);
+  // the ragged edges of a chunk are taken one element at a time.
+  double acc = 0.0;
+  int64_t head = lo;
+  while (head < hi && (reinterpret_cast<uintptr_t>(v + head) & 15) != 0) ++head;
+  const int64_t n4 = (hi - head) / 4;
+  for (int64_t i = lo + threadIdx.x; i < head; i += kSumThreads) {
+    const float x = v[i];
+    if (x == x) acc += static_cast<double>(x);
+  }
+  double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+  const float4* v4 = reinterpret_cast<const float4*>(v + head);
+#pragma unroll 4
+  for (int64_t i = threadIdx.x; i < n4; i += kSumThreads) {   // several 16-byte loads in flight per thread
+    const float4 x = v4[i];
+    if (x.x == x.x) a0 += static_cast<double>(x.x);
+    if (x.y == x.y) a1 += static_cast<double>(x.y);
+    if (x.z == x.z) a2 += static_cast<double>(x.z);
+    if (x.w == x.w) a3 += static_cast<double>(x.w);
+  }
+  acc += (a0 + a1) + (a2 + a3);
+  for (int64_t i = head + 4 * n4 + threadIdx.x; i < hi; i += kSumThreads) {
+    const float x = v[i];
+    if (x == x) acc += static_cast<double>(x);
+  }
+  const double t = block_sum(acc);
+  if (threadIdx.x == 0) partial[plane * kPlaneBlocks + blockIdx.x] = t;
+}
+
+// Stage 1 of the group sum: values carry a small group key each (the device row of an MLP
+// query); a block sums a fixed contiguous chunk into one accumulator per group.  Keys at or
+// above n_groups and NaN values are skipped.
+constexpr int kGroupBlocks = 256;
+constexpr int kMaxGroups = 8;     // groups per pass; more groups take more passes
+
+__global__ void __launch_bounds__(kSumThreads)
+group_partial_kernel(const float* __restrict__ values, const uint8_t* __restrict__ keys, int64_t n,
+                     int32_t group0, int32_t n_groups, double* __restrict__ partial) {
+  hb_grid_dependency_wait();
+  const int64_t chunk = (n + kGroupBlocks - 1) / kGroupBlocks;
+  const int64_t lo = static_cast<int64_t>(blockIdx.x) * chunk;
+  const int64_t hi = lo + chunk < n ? lo + chunk : n;
+  double acc[kMaxGroups];
+#pragma unroll
+  for (int g = 0; g < kMaxGroups; ++g) acc[g] = 0.0;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += kSumThreads) {
+    const float x = values[i];
+    const int key = static_cast<int>(keys[i]) - group0;
+    const double v = x == x ? static_cast<double>(x) : 0.0;
+#pragma unroll
+    for (int g = 0; g < kMaxGroups; ++g) acc[g] += key == g ? v : 0.0;
+  }
+#pragma unroll
+  for (int g = 0; g < kMaxGroups; ++g) {
+    const double t = block_sum(acc[g]);
+    if (threadIdx.x == 0 && g < n_groups) partial[g * kGroupBlocks + blockIdx.x] = t;
+  }
+}
+
+}  // namespace
