@@ -39,3 +39,32 @@ def predict(weights, op_features, device_rows, device_features, mu, sigma, dtype
         xn = normalise(op_features[i:i + chunk], device_rows[i:i + chunk], device_features, mu, sigma)
         outs.append(forward(weights, xn, dtype))
     return np.concatenate(outs) if outs else np.zeros((0,), dtype)
+
+
+def bf16_round(x):
+    """float32 values rounded to the nearest bfloat16 (ties to even), returned as float32."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = (u + (((u >> np.uint32(16)) & np.uint32(1)) + np.uint32(0x7FFF))) & np.uint32(0xFFFF0000)
+    return r.view(np.float32)
+
+
+def forward_bf16(weights, x_norm, depth=None):
+    """The arithmetic of the device's bf16 mode, replayed in numpy: where the kernel rounds to
+    bfloat16 (hidden-layer weights and activations) this rounds too, everything else is float32.
+    fc1 keeps x and w as bf16 hi + lo parts and adds the products hi.hi + lo.hi + hi.lo; fc2 works on
+    the unrounded float32 activations of the last hidden layer.  The only difference left to the
+    device is the order of the float32 additions inside a dot product.  Not part of the reference:
+    it pins the kernel far more tightly than a comparison with the float64 forward can."""
+    x = np.asarray(x_norm).astype(np.float32)
+    w1 = weights["fc1_w"].astype(np.float32)
+    xh, wh = bf16_round(x), bf16_round(w1)
+    xl, wl = bf16_round(x - xh), bf16_round(w1 - wh)
+    z = (xh @ wh.T + xl @ wh.T + xh @ wl.T).astype(np.float32) + weights["fc1_b"].astype(np.float32)
+    h = np.maximum(z, 0)
+    n_hidden = weights["hidden_w"].shape[0] if depth is None else depth
+    for L in range(n_hidden):
+        a = bf16_round(h)
+        w = bf16_round(weights["hidden_w"][L].astype(np.float32))
+        h = np.maximum((a @ w.T).astype(np.float32) + weights["hidden_b"][L].astype(np.float32), 0)
+    return (h @ weights["fc2_w"].astype(np.float32).reshape(-1) +
+            weights["fc2_b"].astype(np.float32).reshape(-1)[0]).astype(np.float32)
