@@ -350,6 +350,8 @@ hb_status hb_peer_connect(hb_peer* handle, const uint8_t* handles);
 hb_status hb_peer_connect_pointers(hb_peer* handle, void* const* mailboxes);
 void* hb_peer_mailbox(hb_peer* handle);
 hb_status hb_peer_set_wait_ns(hb_peer* handle, int64_t wait_ns);
+/* Frees the mailbox.  Peers store into it during their exchanges: destroy only after
+ * every rank has finished its last exchange (meet on the host first). */
 void hb_peer_destroy(hb_peer* handle);
 /* Synchronises; HB_ERR_DEVICE_TIMEOUT (reported once, then cleared) when a wait ran out. */
 hb_status hb_peer_status(hb_peer* handle, int32_t* device_status);
