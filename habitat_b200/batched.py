@@ -5,6 +5,7 @@ C ABI (include/habitat_b200.h).  torch is used for device memory and streams
 only; all arithmetic happens in the library's sm_100a kernels.
 """
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
@@ -22,6 +23,24 @@ def _require_cuda(t, dtype, name):
     if not t.is_contiguous():
         raise ValueError("%s must be contiguous" % name)
     return t
+
+
+# HABITAT_B200_NVTX=1 wraps every native call in an NVTX range named after it, so that a timeline
+# shows which entry point a kernel belongs to.
+_NVTX = os.environ.get("HABITAT_B200_NVTX", "") not in ("", "0")
+
+
+class _Range:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if _NVTX:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if _NVTX:
+            torch.cuda.nvtx.range_pop()
 
 
 def _ptr(t):
@@ -132,8 +151,9 @@ def wave_scale(kernels: KernelBatch, origin, dests: Sequence, dest_regs=None, me
     dest_rows = (ctypes.c_int32 * D)(*rows[1:])
     stream = _native.current_stream_ptr()
     if metrics is None:
-        st = lib.hb_wave_scale(ctypes.byref(soa), K, rows[0], dest_rows, D, _ptr(dest_regs),
-                               ctypes.byref(wout), stream)
+        with _Range("hb_wave_scale"):
+            st = lib.hb_wave_scale(ctypes.byref(soa), K, rows[0], dest_rows, D, _ptr(dest_regs),
+                                   ctypes.byref(wout), stream)
     else:
         _require_cuda(metrics.flop_efficiency_pct, torch.float64, "flop_efficiency_pct")
         _require_cuda(metrics.dram_read_bytes, torch.float64, "dram_read_bytes")
@@ -141,8 +161,9 @@ def wave_scale(kernels: KernelBatch, origin, dests: Sequence, dest_regs=None, me
         _require_cuda(metrics.has_metrics, torch.uint8, "has_metrics")
         m = _native.KernelMetrics(_ptr(metrics.flop_efficiency_pct), _ptr(metrics.dram_read_bytes),
                                   _ptr(metrics.dram_write_bytes), _ptr(metrics.has_metrics))
-        st = lib.hb_wave_scale_metrics(ctypes.byref(soa), ctypes.byref(m), K, rows[0], dest_rows, D,
-                                       _ptr(dest_regs), ctypes.byref(wout), stream)
+        with _Range("hb_wave_scale_metrics"):
+            st = lib.hb_wave_scale_metrics(ctypes.byref(soa), ctypes.byref(m), K, rows[0], dest_rows, D,
+                                           _ptr(dest_regs), ctypes.byref(wout), stream)
     _native.check(st)
     return out
 
@@ -224,8 +245,9 @@ class MLPHandle:
             raise ValueError("device_row must have Q entries")
         if out is None:
             out = torch.empty((Q,), dtype=torch.float32, device=op_features.device)
-        _native.check(lib.hb_mlp_predict(self._handle, _ptr(op_features), _ptr(device_row), Q,
-                                         _ptr(out), _native.current_stream_ptr()))
+        with _Range("hb_mlp_predict"):
+            _native.check(lib.hb_mlp_predict(self._handle, _ptr(op_features), _ptr(device_row), Q,
+                                             _ptr(out), _native.current_stream_ptr()))
         return out
 
     def predict_host(self, op_features, device_row):

@@ -202,3 +202,14 @@ def test_workloads_are_seeded():
     assert f.shape == (50, 7) and d.max() < 6 and f[:, 4].min() >= 32
     mu, sigma = workloads.batch_mu_sigma(f, d)
     assert mu.shape == (11,) and (sigma > 0).all()
+
+
+def test_precision_knob(monkeypatch):
+    from habitat_b200.analysis.predictor import Predictor
+    assert Predictor()._precision == "bf16"
+    monkeypatch.setenv("HABITAT_B200_PRECISION", "bf16x3")
+    assert Predictor()._precision == "bf16x3"
+    assert Predictor(precision="bf16")._precision == "bf16"
+    monkeypatch.setenv("HABITAT_B200_PRECISION", "fp64")
+    with pytest.raises(ValueError):
+        Predictor()
