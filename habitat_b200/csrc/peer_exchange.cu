@@ -304,7 +304,7 @@ extern "C" hb_status hb_plane_sum_allreduce(hb_peer* h, const float* values, int
   if (st != HB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   ++h->seq;
-  HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(kPlaneBlocks, n_planes), dim3(kSumThreads), 0, s,
+  HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(n_planes, kPlaneBlocks), dim3(kSumThreads), 0, s,
                                     values, plane_len, h->partial));
   HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n_planes), dim3(kSumThreads), 0, s,
                                     static_cast<const double*>(h->partial), out, view_of(h), 3));

@@ -132,7 +132,7 @@ extern "C" hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_
   const hb_status st = scratch_for_current_device(static_cast<size_t>(n_planes), false, &sc);
   if (st != HB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(kPlaneBlocks, n_planes), dim3(kSumThreads), 0, s,
+  HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(n_planes, kPlaneBlocks), dim3(kSumThreads), 0, s,
                                     values, plane_len, sc.plane));
   HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel, dim3(n_planes), dim3(kSumThreads), 0, s,
                                     static_cast<const double*>(sc.plane), out));
@@ -227,7 +227,7 @@ extern "C" hb_status hb_plane_sum_static(const float* values, int64_t plane_len,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // Stage 1 writes every partial that stage 2 reads, so nothing in the scratch
   // has to start at zero; whatever the previous call left there is overwritten.
-  plane_partial_kernel<<<dim3(kPlaneBlocks, n_planes), kSumThreads, 0, s>>>(values, plane_len, scratch);
+  plane_partial_kernel<<<dim3(n_planes, kPlaneBlocks), kSumThreads, 0, s>>>(values, plane_len, scratch);
   HB_CUDA_TRY(cudaGetLastError());
   plane_final_kernel<<<n_planes, kSumThreads, 0, s>>>(scratch, out);
   HB_CUDA_TRY(cudaGetLastError());

@@ -39,10 +39,14 @@ __global__ void __launch_bounds__(kSumThreads)
 plane_partial_kernel(const float* __restrict__ values, int64_t plane_len,
                      double* __restrict__ partial) {
   hb_grid_dependency_wait();
-  const int plane = blockIdx.y;
+  const int plane = blockIdx.x;     // grid (planes, chunks): the planes' ends are visited together
   const float* v = values + static_cast<int64_t>(plane) * plane_len;
+  // Blocks take the chunks from the end of the plane backwards: the kernel that has just written the
+  // plane wrote its end last, so that part is the likeliest to be still in L2.  The partial sum of a
+  // chunk lands in the chunk's own slot, so the result does not depend on this order.
+  const int chunk_id = kPlaneBlocks - 1 - static_cast<int>(blockIdx.y);
   const int64_t chunk = (plane_len + kPlaneBlocks - 1) / kPlaneBlocks;
-  const int64_t lo = static_cast<int64_t>(blockIdx.x) * chunk;
+  const int64_t lo = static_cast<int64_t>(chunk_id) * chunk;
   const int64_t hi = lo + chunk < plane_len ? lo + chunk : plane_len;
   // The bulk of a chunk goes through 16-byte loads with four independent accumulators (the
   // assignment of elements to accumulators is fixed, so the result is the same for every launch);
@@ -71,7 +75,7 @@ plane_partial_kernel(const float* __restrict__ values, int64_t plane_len,
     if (x == x) acc += static_cast<double>(x);
   }
   const double t = block_sum(acc);
-  if (threadIdx.x == 0) partial[plane * kPlaneBlocks + blockIdx.x] = t;
+  if (threadIdx.x == 0) partial[plane * kPlaneBlocks + chunk_id] = t;
 }
 
 // Stage 1 of the group sum: values carry a small group key each (the device row of an MLP
