@@ -367,24 +367,14 @@ def case_config2(ctx, small=True, large=True):
         with torch.cuda.graph(g_kernel, stream=ctx.stream):
             for i in range(reps):
                 batched.wave_scale(kbs[i % CONFIG2_SETS], ctx.origin, ctx.bench_devs, out=outs[i % CONFIG2_SETS])
-        # a step = the kernel plus the per-destination totals; the totals of step i run on a second
-        # stream beside the kernel of step i + 1 (a buffer set is reused only after its totals were taken)
-        side = torch.cuda.Stream()
+        # a step = the kernel, whose blocks add up their own results, plus the final stage of the
+        # per-destination totals
+        parts = [batched.WavePartials(CONFIG2_K, WAVE_D) for _ in range(CONFIG2_SETS)]
         with torch.cuda.graph(g_step, stream=ctx.stream):
-            waved = [torch.cuda.Event() for _ in range(reps)]
-            summed = [torch.cuda.Event() for _ in range(reps)]
-            side.wait_stream(ctx.stream)
             for i in range(reps):
                 s = i % CONFIG2_SETS
-                if i >= CONFIG2_SETS:
-                    ctx.stream.wait_event(summed[i - CONFIG2_SETS])
-                batched.wave_scale(kbs[s], ctx.origin, ctx.bench_devs, out=outs[s])
-                waved[i].record(ctx.stream)
-                with torch.cuda.stream(side):
-                    side.wait_event(waved[i])
-                    batched.plane_sum(outs[s].scaled_ns, out=totals[i])
-                    summed[i].record(side)
-            ctx.stream.wait_stream(side)
+                batched.wave_scale(kbs[s], ctx.origin, ctx.bench_devs, out=outs[s], partials=parts[s])
+                parts[s].totals(out=totals[i])
         kern_ms, n_k = replay_timed(ctx, g_kernel, reps)
         step_ms, n_s = replay_timed(ctx, g_step, reps)
         pairs = CONFIG2_K * WAVE_D
@@ -396,7 +386,7 @@ def case_config2(ctx, small=True, large=True):
                "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                "us_per_step": step_ms * 1e3, "steps_timed": n_s,
                "pairs_per_s_step": pairs / (step_ms * 1e-3)}
-        ctx.launches += n_k + 3 * n_s
+        ctx.launches += n_k + 2 * n_s
         del kbs, outs, g_kernel, g_step
         if large:
             out["large_batch"] = case_config2_large(ctx)
@@ -421,6 +411,46 @@ def case_config2_large(ctx):
         ctx.launches += n_b
         return {"kernels": big_k, "us_per_launch": big_ms * 1e3, "achieved": big_gbs,
                 "frac": big_gbs / ctx.peaks["hbm_gbs"], "launches_timed": n_b}
+
+
+def case_config2_totals(ctx):
+    """Per-destination totals of the predicted times, two ways, per launch size: the table kernel
+    followed by the two-stage plane sum over its results, and the table kernel whose blocks add up
+    their own results followed by the final stage alone.  Graph replay, four rotating buffer sets."""
+    torch = ctx.torch
+    from habitat_b200 import batched, workloads
+    rows = []
+    with torch.cuda.stream(ctx.stream):
+        for K in (CONFIG2_K, workloads.SWEEP_KERNELS // 16 * 2, workloads.SWEEP_KERNELS):
+            sets, reps = 4, 20
+            kbs = [batched.KernelBatch.from_numpy(workloads.make_kernels(K, 1002 + 17 * s)) for s in range(sets)]
+            parts = [batched.WavePartials(K, WAVE_D) for _ in range(sets)]
+            outs = [batched.wave_scale(kbs[s], ctx.origin, ctx.bench_devs, partials=parts[s]) for s in range(sets)]
+            totals = torch.zeros((reps, WAVE_D), dtype=torch.float64, device="cuda")
+            parts[0].totals(out=totals[0])
+            batched.plane_sum(outs[0].scaled_ns, out=totals[1])
+            torch.cuda.synchronize()
+            row = {"kernels": K, "first_stage_sums_per_destination": parts[0].per_plane}
+            for name, fused, final in (("kernel", False, False), ("kernel_then_plane_sum", False, True),
+                                       ("kernel_with_block_sums", True, False),
+                                       ("kernel_with_block_sums_then_final_stage", True, True)):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=ctx.stream):
+                    for i in range(reps):
+                        q = i % sets
+                        batched.wave_scale(kbs[q], ctx.origin, ctx.bench_devs, out=outs[q],
+                                           partials=parts[q] if fused else None)
+                        if final and fused:
+                            parts[q].totals(out=totals[i])
+                        elif final:
+                            batched.plane_sum(outs[q].scaled_ns, out=totals[i])
+                ms, n = replay_timed(ctx, g, reps)
+                row["us_" + name] = ms * 1e3
+                ctx.launches += n * (1 + (2 if final and not fused else int(final)))
+                del g
+            rows.append(row)
+            del kbs, parts, outs
+    return {"workload": "per-destination totals of the predicted times, 6 device rows", "launch_sizes": rows}
 
 
 def case_config3(ctx):
@@ -546,12 +576,16 @@ class Sweep:
         self.ops = workloads.SWEEP_OPS
         hd = ctx.hd
         if klo is None:
-            klo, khi = hd.shard_bounds_aligned(workloads.SWEEP_KERNELS, ctx.rank, ctx.world, 2)
+            # cut on the 256 kernels a block of the table kernel takes: a shard's first-stage sums are
+            # then the whole batch's, and the sharded totals differ from one GPU's only by the order of
+            # the last float64 additions
+            klo, khi = hd.shard_bounds_aligned(workloads.SWEEP_KERNELS, ctx.rank, ctx.world, 256)
             qlo, qhi = hd.shard_bounds_aligned(workloads.SWEEP_QUERIES, ctx.rank, ctx.world, 128)
         self.klo, self.khi, self.qlo, self.qhi = klo, khi, qlo, qhi
         self.host_k = workloads.sweep_kernels(klo, khi)
         self.kb = batched.KernelBatch.from_numpy(self.host_k)
-        self.out = batched.wave_scale(self.kb, ctx.origin, ctx.bench_devs)
+        self.partials = batched.WavePartials(khi - klo, WAVE_D)
+        self.out = batched.wave_scale(self.kb, ctx.origin, ctx.bench_devs, partials=self.partials)
         self.weights, self.stats, self.host_q = {}, {}, {}
         self.handles = handles if handles is not None else {}
         self.d_f, self.d_r, self.d_o = {}, {}, {}
@@ -571,8 +605,9 @@ class Sweep:
         self.ev = []
 
     def step(self, i, timed=True, via=None):
-        """One pass over the shard: wave-scaling phase, then the MLP phase; each ends with the
-        all-reduce of its totals (via "peer": inside the final stage of the reductions, through
+        """One pass over the shard: wave-scaling phase (the kernel's blocks add up their own results;
+        a final stage turns the block sums into the [6] totals), then the MLP phase; each ends with
+        the all-reduce of its totals (via "peer": inside the final stage of the reductions, through
         peer memory; via "nccl": one NCCL all-reduce per phase).  Events bracket the phases and
         the dominant kernels."""
         ctx, torch = self.ctx, self.ctx.torch
@@ -584,13 +619,13 @@ class Sweep:
         self.flush.zero_()                     # the shard's data of the step before must not sit in L2
         if timed:
             ev["w0"].record(s)
-        batched.wave_scale(self.kb, ctx.origin, ctx.bench_devs, out=self.out)
+        batched.wave_scale(self.kb, ctx.origin, ctx.bench_devs, out=self.out, partials=self.partials)
         if timed:
             ev["k1"].record(s)
         if via == "peer":
-            ctx.peer.plane_sum(self.out.scaled_ns, out=tot[:WAVE_D])
+            ctx.peer.partials_sum(self.partials, out=tot[:WAVE_D])
         else:
-            batched.plane_sum(self.out.scaled_ns, out=tot[:WAVE_D])
+            self.partials.totals(out=tot[:WAVE_D])
             if via == "nccl":
                 ctx.dist.all_reduce(tot[:WAVE_D])
         if timed:
@@ -617,7 +652,7 @@ class Sweep:
             ev["m1"].record(s)
             ev["pk"] = pk
             self.ev.append(ev)
-        ctx.launches += 3 + 3 * len(self.ops)
+        ctx.launches += 2 + 3 * len(self.ops)
 
     def phase_ms(self):
         w = sum(e["w0"].elapsed_time(e["w1"]) for e in self.ev)
@@ -923,7 +958,7 @@ def main():
     ap.add_argument("--totals", default="peer", choices=["peer", "nccl"],
                     help="how the per-step totals are summed across GPUs")
     ap.add_argument("--case", default="all",
-                    choices=["all", "config2", "config2-large", "config2-status", "config2-regs", "config2-metrics",
+                    choices=["all", "config2", "config2-large", "config2-totals", "config2-status", "config2-regs", "config2-metrics",
                              "config3", "config1"],
                     help="run one kernel-only sub-entry alone and print it (for profilers)")
     args = ap.parse_args()
@@ -938,6 +973,7 @@ def main():
         if ctx.rank == 0:
             fn = {"config2": lambda: case_config2(ctx, large=False),
                   "config2-large": lambda: case_config2(ctx, small=False),
+                  "config2-totals": lambda: case_config2_totals(ctx),
                   "config2-status": lambda: case_config2_inputs(ctx, "status"),
                   "config2-regs": lambda: case_config2_inputs(ctx, "regs"),
                   "config2-metrics": lambda: case_config2_inputs(ctx, "metrics"),
@@ -1038,7 +1074,8 @@ def main():
         "config": {
             "workload": SWEEP_WORKLOAD,
             "step": "one pass over the whole batch: a wave-scaling phase (the table kernel on the rank's kernels, "
-                    "per-destination totals, all-reduce of the [6] totals) and an MLP phase (the four predictors "
+                    "whose blocks add up their own results; a final stage over the block sums that ends in the "
+                    "all-reduce of the [6] totals) and an MLP phase (the four predictors "
                     "on the rank's queries, per-device totals of each, all-reduce of the [4 x 6] totals); `value` "
                     "is pairs over the wave-scaling phases, `mlp.value` predictions over the MLP phases, "
                     "`ms_per_step` the whole step, all max over ranks, CUDA events on the launching stream",

@@ -119,6 +119,15 @@ EXPORTS = {
     "hb_group_sum_allreduce": (ctypes.c_int32, [
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p,
         ctypes.c_void_p]),
+    "hb_wave_scale_partials_len": (ctypes.c_int64, [ctypes.c_int64]),
+    "hb_wave_scale_partials": (ctypes.c_int32, [
+        ctypes.POINTER(KernelSoA), ctypes.c_int64, ctypes.c_int32,
+        ctypes.POINTER(ctypes.c_int32), ctypes.c_int32, ctypes.c_void_p,
+        ctypes.POINTER(WaveOut), ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32), ctypes.c_void_p]),
+    "hb_partials_sum": (ctypes.c_int32, [
+        ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "hb_partials_sum_allreduce": (ctypes.c_int32, [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
     "hb_peer_allreduce": (ctypes.c_int32, [
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]),
 }

@@ -103,13 +103,41 @@ class WaveResult:
     limits: Optional[torch.Tensor] = None   # [D + 1, 4, K] int32
 
 
+class WavePartials:
+    """Room for the first stage of the per-destination totals of a wave_scale call over up to K
+    kernels and D destinations (hb_wave_scale_partials): pass it as `partials=`, then `totals()`
+    (or PeerTotals.partials_sum across GPUs) gives the D float64 totals without a second pass over
+    the [D, K] results when the launch takes the table kernel."""
+
+    def __init__(self, K, D, device="cuda"):
+        self.K, self.D = int(K), int(D)
+        n = int(_native.load().hb_wave_scale_partials_len(self.K))
+        self.buffer = torch.empty((self.D * n,), dtype=torch.float64, device=device)
+        self.per_plane = 0      # first-stage sums per destination left by the last call
+        self.n_planes = 0
+
+    def totals(self, out=None):
+        """[D] float64 totals of the last wave_scale call that was given this object."""
+        if out is None:
+            out = torch.empty((self.n_planes,), dtype=torch.float64, device=self.buffer.device)
+        _require_cuda(out, torch.float64, "out")
+        if out.numel() != self.n_planes:
+            raise ValueError("out must have one entry per destination")
+        with _Range("hb_partials_sum"):
+            _native.check(_native.load().hb_partials_sum(_ptr(self.buffer), self.per_plane, self.n_planes,
+                                                         _ptr(out), _native.current_stream_ptr()))
+        return out
+
+
 def wave_scale(kernels: KernelBatch, origin, dests: Sequence, dest_regs=None, metrics=None,
-               want_status=False, want_limits=False, out: Optional[WaveResult] = None):
+               want_status=False, want_limits=False, out: Optional[WaveResult] = None,
+               partials: Optional[WavePartials] = None):
     """Wave-scales K kernels measured on `origin` to every device in `dests`.
 
     origin / dests are DeviceProperties.  dest_regs is an optional [D, K] int16
     tensor of per-destination register counts (-1: use the kernel's own).
     With `metrics`, gamma is computed on the device per (kernel, destination).
+    With `partials` the call also leaves the first stage of the per-destination totals there.
     Queued on the current stream; does not synchronise.
     """
     lib = _native.load()
@@ -150,7 +178,18 @@ def wave_scale(kernels: KernelBatch, origin, dests: Sequence, dest_regs=None, me
                            _ptr(out.limits))
     dest_rows = (ctypes.c_int32 * D)(*rows[1:])
     stream = _native.current_stream_ptr()
-    if metrics is None:
+    if partials is not None:
+        if metrics is not None:
+            raise ValueError("partials are not available together with metrics")
+        if K > partials.K or D > partials.D:
+            raise ValueError("partials were sized for fewer kernels or destinations")
+        per_plane = ctypes.c_int32(0)
+        with _Range("hb_wave_scale_partials"):
+            st = lib.hb_wave_scale_partials(ctypes.byref(soa), K, rows[0], dest_rows, D, _ptr(dest_regs),
+                                            ctypes.byref(wout), _ptr(partials.buffer), ctypes.byref(per_plane),
+                                            stream)
+        partials.per_plane, partials.n_planes = int(per_plane.value), D
+    elif metrics is None:
         with _Range("hb_wave_scale"):
             st = lib.hb_wave_scale(ctypes.byref(soa), K, rows[0], dest_rows, D, _ptr(dest_regs),
                                    ctypes.byref(wout), stream)

@@ -106,18 +106,18 @@ __device__ __forceinline__ double peer_collect(const PeerView& pv, int i, double
   return total;
 }
 
-// Final stage + exchange: block i adds the 256 partial sums of value i, publishes the result
+// Final stage + exchange: block i adds the `per_plane` partial sums of value i, publishes the result
 // to every rank and gathers the ranks' results.  phase: 1 publish only, 2 gather only (of a
 // value published by an earlier launch: `out` holds it), 3 both (the normal, fused call).
-__global__ void __launch_bounds__(kSumThreads)
-peer_final_exchange_kernel(const double* __restrict__ partial, double* __restrict__ out, const PeerView pv,
-                           int phase) {
+__global__ void __launch_bounds__(kFinalThreadsMax)
+peer_final_exchange_kernel(const double* __restrict__ partial, int per_plane, double* __restrict__ out,
+                           const PeerView pv, int phase) {
   hb_grid_dependency_wait();
   __shared__ double sh[kPeerMaxWorld];
   const int i = blockIdx.x;
   double mine = 0.0;
   if (phase & 1) {
-    const double v = partial ? partial[i * kPlaneBlocks + threadIdx.x] : 0.0;
+    const double v = partial ? partials_share(partial + static_cast<size_t>(i) * per_plane, per_plane) : 0.0;
     const double t = block_sum(v);
     if (threadIdx.x == 0) sh[0] = partial ? t : out[i];
     __syncthreads();
@@ -307,7 +307,23 @@ extern "C" hb_status hb_plane_sum_allreduce(hb_peer* h, const float* values, int
   HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(n_planes, kPlaneBlocks), dim3(kSumThreads), 0, s,
                                     values, plane_len, h->partial));
   HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n_planes), dim3(kSumThreads), 0, s,
-                                    static_cast<const double*>(h->partial), out, view_of(h), 3));
+                                    static_cast<const double*>(h->partial), kPlaneBlocks, out, view_of(h), 3));
+  return HB_OK;
+}
+
+extern "C" hb_status hb_partials_sum_allreduce(hb_peer* h, const double* partials, int32_t per_plane,
+                                               int32_t n_planes, double* out, void* stream) {
+  if (per_plane < 0 || n_planes < 1 || !out || (per_plane > 0 && !partials)) {
+    hb::set_error("hb_partials_sum_allreduce: bad arguments");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  const hb_status st = check_call(h, "hb_partials_sum_allreduce", n_planes);
+  if (st != HB_OK) return st;
+  ++h->seq;
+  // an empty shard (per_plane 0) still takes part in the exchange, with zeros
+  HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n_planes), dim3(final_threads(per_plane)), 0,
+                                    static_cast<cudaStream_t>(stream), per_plane > 0 ? partials : h->partial, per_plane,
+                                    out, view_of(h), 3));
   return HB_OK;
 }
 
@@ -324,7 +340,7 @@ extern "C" hb_status hb_group_sum_allreduce(hb_peer* h, const float* values, con
   HB_CUDA_TRY(hb::launch_overlapped(group_partial_kernel, dim3(kGroupBlocks), dim3(kSumThreads), 0, s, values,
                                     keys, n, 0, n_groups, h->partial));
   HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n_groups), dim3(kSumThreads), 0, s,
-                                    static_cast<const double*>(h->partial), out, view_of(h), 3));
+                                    static_cast<const double*>(h->partial), kGroupBlocks, out, view_of(h), 3));
   return HB_OK;
 }
 
@@ -338,6 +354,6 @@ extern "C" hb_status hb_peer_allreduce(hb_peer* h, double* values, int32_t n, in
   if (phase & 1) ++h->seq;      // a gather-only call belongs to the publish before it
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n), dim3(kSumThreads), 0, s,
-                                    static_cast<const double*>(nullptr), values, view_of(h), phase));
+                                    static_cast<const double*>(nullptr), 0, values, view_of(h), phase));
   return HB_OK;
 }

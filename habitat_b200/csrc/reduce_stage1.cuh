@@ -16,20 +16,52 @@ __device__ __forceinline__ double warp_sum(double v) {
   return v;
 }
 
-// Block-wide sum of one value per thread; valid in thread 0.
+// Block-wide sum of one value per thread (blocks of 32..1024 threads); valid in thread 0.
 __device__ __forceinline__ double block_sum(double v) {
-  __shared__ double s[kSumThreads / 32];
+  __shared__ double s[32];
   v = warp_sum(v);
   if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
   __syncthreads();
   double t = 0.0;
   if (threadIdx.x < 32) {
-    t = threadIdx.x < kSumThreads / 32 ? s[threadIdx.x] : 0.0;
+    t = threadIdx.x < (blockDim.x >> 5) ? s[threadIdx.x] : 0.0;
     t = warp_sum(t);
   }
   __syncthreads();
   return t;
 }
+
+// This thread's share of the `per_plane` first-stage sums of one plane: elements threadIdx.x,
+// threadIdx.x + blockDim.x, ... in eight interleaved accumulators, eight loads in flight (a
+// fixed assignment for a given block size, so the value does not depend on scheduling).  With
+// per_plane <= blockDim.x it is the thread's own element.
+__device__ __forceinline__ double partials_share(const double* __restrict__ q, int per_plane) {
+  constexpr int kWays = 8;   // sixteen measured slower: accumulators and loads in flight no longer fit the registers of a 1024-thread block
+  double a[kWays];
+#pragma unroll
+  for (int u = 0; u < kWays; ++u) a[u] = 0.0;
+  const int n = blockDim.x;
+  int i = threadIdx.x;
+  for (; i + (kWays - 1) * n < per_plane; i += kWays * n) {
+#pragma unroll
+    for (int u = 0; u < kWays; ++u) a[u] += q[i + u * n];
+  }
+#pragma unroll
+  for (int u = 0; u < kWays - 1; ++u)
+    if (i + u * n < per_plane) a[u] += q[i + u * n];
+#pragma unroll
+  for (int w = kWays / 2; w > 0; w >>= 1) {
+#pragma unroll
+    for (int u = 0; u < w; ++u) a[u] += a[u + w];
+  }
+  return a[0];
+}
+
+// Threads per block of a final stage over `per_plane` first-stage sums: the plane sums' own 256
+// first-stage sums keep the block size their results were defined with; long lists (one sum per
+// block of the wave-scaling kernel) get 1024 threads so that more loads are in flight.
+constexpr int kFinalThreadsMax = 1024;
+inline int final_threads(int per_plane) { return per_plane > 2 * kSumThreads ? kFinalThreadsMax : kSumThreads; }
 
 // Stage 1 of the plane sum: a fixed number of blocks per plane, each summing a
 // fixed contiguous chunk; NaN entries (pairs the reference raises on) skipped.

@@ -22,6 +22,7 @@
 
 #include "hb_common.h"
 #include "occupancy.cuh"
+#include "reduce_stage1.cuh"
 
 namespace {
 
@@ -80,6 +81,7 @@ struct Ptrs {
   uint32_t* origin_waves;
   uint8_t* status;
   int32_t* limits;
+  double* block_sums;   // table kernel with fused totals: [D][blocks] sums of each block's results
 };
 
 // Per-SM block count ceil(nb / sms) for a kernel that fits in one wave.
@@ -483,12 +485,24 @@ __device__ __forceinline__ void store_byte_pair(uint8_t* q, uint32_t pair_word, 
   }
 }
 
-template <int VEC, bool EXT, bool ALIGNED, int NP, int NS>
+// TOT: every block also adds up its own results per destination (float64, fixed order, NaN results
+// skipped like the plane sums do) and leaves the sums in p.block_sums[d * gridDim.x + block], so
+// the totals of a launch need no second pass over the [D x K] plane.  A thread parks its two
+// results per destination in shared memory; at the end sixteen lanes per destination add the
+// block's 256 values.  Needs a grid that covers the batch in one pass and D <= kTotMaxD.
+constexpr int kTotMaxD = kLutThreads / 16;
+
+template <int VEC, bool EXT, bool ALIGNED, int NP, int NS, bool TOT = false>
 __global__ void __launch_bounds__(kLutThreads, EXT ? 8 : 12)
 wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
+  static_assert(!TOT || (VEC == 2 && ALIGNED && !EXT), "fused totals: aligned two-record variant only");
+  __shared__ float2 s_tot[TOT ? kTotMaxD : 1][TOT ? kLutThreads : 1];
   hb_grid_dependency_wait();
   const uint32_t K = lp.K;
   const int D = lp.D;
+  if (TOT && (blockIdx.x * kLutThreads + threadIdx.x) * VEC >= K) {
+    for (int d = 0; d < D; ++d) s_tot[d][threadIdx.x] = make_float2(0.0f, 0.0f);   // threads past the end
+  }
   const uint8_t* __restrict__ tab_t = reinterpret_cast<const uint8_t*>(g_lut_t);
   const uint32_t stride = gridDim.x * (kLutThreads * VEC);
   const bool with_regs = EXT && p.dest_regs != nullptr;
@@ -656,7 +670,28 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
       store_pair<uint32_t, VEC, ALIGNED>(p.dest_waves + base, wavv, pair);
       store_byte_pair<VEC, ALIGNED>(p.dest_occ + base, occ2, pair);
       if (with_status) store_byte_pair<VEC, ALIGNED>(p.status + base, st2, pair);
+      if (TOT) s_tot[d][threadIdx.x] = make_float2(outv.v[0], outv.v[VEC - 1]);
     }
+  }
+  if (TOT) {
+    __syncthreads();
+    const int d = threadIdx.x >> 4, j = threadIdx.x & 15;
+    double acc = 0.0;
+    if (d < D) {
+      const float4* row = reinterpret_cast<const float4*>(s_tot[d]);
+#pragma unroll
+      for (int i = 0; i < kLutThreads / 32; ++i) {
+        const float4 x = row[j + 16 * i];
+        const double a0 = static_cast<double>(x.x == x.x ? x.x : 0.0f);   // NaN: no prediction for the pair
+        const double a1 = static_cast<double>(x.y == x.y ? x.y : 0.0f);
+        const double a2 = static_cast<double>(x.z == x.z ? x.z : 0.0f);
+        const double a3 = static_cast<double>(x.w == x.w ? x.w : 0.0f);
+        acc += (a0 + a1) + (a2 + a3);
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) acc += __shfl_down_sync(0xFFFFFFFFu, acc, o, 16);
+    if (j == 0 && d < D) p.block_sums[static_cast<size_t>(d) * gridDim.x + blockIdx.x] = acc;
   }
 }
 
@@ -758,24 +793,36 @@ int class_of(int* rows, int* n, int row, Same same) {
   return (*n)++;
 }
 
-template <int VEC, bool EXT, bool ALIGNED, int NP, int NS>
+template <int VEC, bool EXT, bool ALIGNED, int NP, int NS, bool TOT = false>
 cudaError_t launch_lut(unsigned grid, cudaStream_t stream, const Ptrs& p, const LutParams& q) {
-  return hb::launch_overlapped(wave_scale_lut_kernel<VEC, EXT, ALIGNED, NP, NS>, dim3(grid), dim3(kLutThreads), 0,
-                               stream, p, q);
+  return hb::launch_overlapped(wave_scale_lut_kernel<VEC, EXT, ALIGNED, NP, NS, TOT>, dim3(grid), dim3(kLutThreads),
+                               0, stream, p, q);
 }
 
-template <int NP>
+template <int NP, bool TOT>
 cudaError_t launch_lut_plain(int ns, unsigned grid, cudaStream_t stream, const Ptrs& p, const LutParams& q) {
   switch (ns) {
-    case 1: return launch_lut<2, false, true, NP, 1>(grid, stream, p, q);
-    case 2: return launch_lut<2, false, true, NP, 2>(grid, stream, p, q);
-    case 3: return launch_lut<2, false, true, NP, 3>(grid, stream, p, q);
-    default: return launch_lut<2, false, true, NP, 4>(grid, stream, p, q);
+    case 1: return launch_lut<2, false, true, NP, 1, TOT>(grid, stream, p, q);
+    case 2: return launch_lut<2, false, true, NP, 2, TOT>(grid, stream, p, q);
+    case 3: return launch_lut<2, false, true, NP, 3, TOT>(grid, stream, p, q);
+    default: return launch_lut<2, false, true, NP, 4, TOT>(grid, stream, p, q);
+  }
+}
+template <bool TOT>
+cudaError_t launch_lut_plain(int np, int ns, unsigned grid, cudaStream_t stream, const Ptrs& p, const LutParams& q) {
+  switch (np) {
+    case 1: return launch_lut_plain<1, TOT>(ns, grid, stream, p, q);
+    case 2: return launch_lut_plain<2, TOT>(ns, grid, stream, p, q);
+    case 3: return launch_lut_plain<3, TOT>(ns, grid, stream, p, q);
+    default: return launch_lut_plain<4, TOT>(ns, grid, stream, p, q);
   }
 }
 
-// Launches wave_scale_lut_kernel when the launch qualifies; false = nothing launched.
-bool try_launch_lut(const Ptrs& p, const LaunchParams& lp, int sm_count, cudaStream_t stream, hb_status* st) {
+// Launches wave_scale_lut_kernel when the launch qualifies; false = nothing launched.  *fused says
+// whether the launch also wrote p.block_sums (one sum per destination and block of the grid).
+bool try_launch_lut(const Ptrs& p, const LaunchParams& lp, int sm_count, cudaStream_t stream, hb_status* st,
+                    bool* fused, unsigned* fused_blocks) {
+  *fused = false;
   static const bool use_lut = [] { const char* e = std::getenv("HB_WAVE_LUT"); return !e || std::atoi(e) != 0; }();
   if (!use_lut || p.limits || lp.D > HB_MAX_DEVICES / 2) return false;
   const int64_t K = lp.K;
@@ -848,13 +895,12 @@ bool try_launch_lut(const Ptrs& p, const LaunchParams& lp, int sm_count, cudaStr
     le = launch_lut<1, false, true, 4, 4>(grid, stream, p, q);
   } else if (!aligned) {
     le = launch_lut<2, false, false, 4, 4>(grid, stream, p, q);
+  } else if (p.block_sums && lp.D <= kTotMaxD && grid == blocks) {
+    le = launch_lut_plain<true>(n_p, n_s, grid, stream, p, q);
+    *fused = true;
+    *fused_blocks = grid;
   } else {
-    switch (n_p) {
-      case 1: le = launch_lut_plain<1>(n_s, grid, stream, p, q); break;
-      case 2: le = launch_lut_plain<2>(n_s, grid, stream, p, q); break;
-      case 3: le = launch_lut_plain<3>(n_s, grid, stream, p, q); break;
-      default: le = launch_lut_plain<4>(n_s, grid, stream, p, q); break;
-    }
+    le = launch_lut_plain<false>(n_p, n_s, grid, stream, p, q);
   }
   t_path = 4;
   const cudaError_t ce = le != cudaSuccess ? le : cudaGetLastError();
@@ -909,14 +955,16 @@ bool try_launch_fast(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream,
 }
 
 template <bool METRICS>
-hb_status launch(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream) {
+hb_status launch_kernel(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream, bool* fused,
+                        unsigned* fused_blocks) {
   int sm_count = 0;
   const hb_status sync_st = sync_gpu(&sm_count);
   if (sync_st != HB_OK) return sync_st;
   const int64_t K = lp.K;
   const bool extra = p.status != nullptr || p.limits != nullptr;
   hb_status fast_st = HB_OK;
-  if (try_launch_lut(p, lp, sm_count, stream, &fast_st)) return fast_st;
+  *fused = false;
+  if (try_launch_lut(p, lp, sm_count, stream, &fast_st, fused, fused_blocks)) return fast_st;
   if (!METRICS && try_launch_fast(p, lp, stream, &fast_st)) return fast_st;
   const bool vec4 = vec4_ok(p, K, !METRICS);
   const int threads = 256;
@@ -937,6 +985,26 @@ hb_status launch(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream) {
   }
   t_path = 1;
   HB_CUDA_TRY(cudaGetLastError());
+  return HB_OK;
+}
+
+// The wave-scaling kernel the launch qualifies for; with p.block_sums also the first stage of the
+// per-destination totals: inside the table kernel when it can (per_plane = blocks of its grid),
+// else by the plane-sum kernel over the results just written (per_plane = kPlaneBlocks).
+template <bool METRICS>
+hb_status launch(const Ptrs& p, const LaunchParams& lp, cudaStream_t stream, int32_t* per_plane = nullptr) {
+  bool fused = false;
+  unsigned fused_blocks = 0;
+  const hb_status st = launch_kernel<METRICS>(p, lp, stream, &fused, &fused_blocks);
+  if (st != HB_OK || !p.block_sums) return st;
+  if (fused) {
+    *per_plane = static_cast<int32_t>(fused_blocks);
+    return HB_OK;
+  }
+  HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(lp.D, kPlaneBlocks), dim3(kSumThreads), 0, stream,
+                                    static_cast<const float*>(p.scaled_ns), static_cast<int64_t>(lp.K),
+                                    p.block_sums));
+  *per_plane = kPlaneBlocks;
   return HB_OK;
 }
 
@@ -1083,6 +1151,32 @@ extern "C" hb_status hb_wave_scale(const hb_kernel_soa* kernels, int64_t K, int3
   if (K == 0) return HB_OK;
   return launch<false>(make_ptrs(kernels, nullptr, dest_regs, out), lp,
                        static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t hb_wave_scale_partials_len(int64_t K) {
+  if (K < 0) return -1;
+  const int64_t blocks = ((K + 1) / 2 + kLutThreads - 1) / kLutThreads;
+  return blocks > kPlaneBlocks ? blocks : kPlaneBlocks;
+}
+
+extern "C" hb_status hb_wave_scale_partials(const hb_kernel_soa* kernels, int64_t K, int32_t origin_row,
+                                            const int32_t* dest_rows_host, int32_t D,
+                                            const int16_t* dest_regs, const hb_wave_out* out,
+                                            double* partials, int32_t* per_plane, void* stream) {
+  hb_status st = check_io(kernels, out, true, K);
+  if (st != HB_OK) return st;
+  if (!per_plane || (K > 0 && !partials)) {
+    hb::set_error("hb_wave_scale_partials: partials / per_plane is NULL");
+    return HB_ERR_INVALID_ARGUMENT;
+  }
+  LaunchParams lp;
+  st = fill_params(&lp, K, origin_row, dest_rows_host, D);
+  if (st != HB_OK) return st;
+  *per_plane = 0;
+  if (K == 0) return HB_OK;
+  Ptrs p = make_ptrs(kernels, nullptr, dest_regs, out);
+  p.block_sums = partials;
+  return launch<false>(p, lp, static_cast<cudaStream_t>(stream), per_plane);
 }
 
 extern "C" hb_status hb_wave_scale_metrics(const hb_kernel_soa* kernels,

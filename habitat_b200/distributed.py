@@ -165,6 +165,17 @@ class PeerTotals:
             self._native.current_stream_ptr()))
         return out
 
+    def partials_sum(self, partials, out=None):
+        """Sum over all ranks of the totals a wave_scale(..., partials=) call left in `partials`
+        (batched.WavePartials) -> [D] float64; a rank whose shard is empty passes partials with
+        per_plane 0 and n_planes set by hand."""
+        if out is None:
+            out = torch.empty((partials.n_planes,), dtype=torch.float64, device=partials.buffer.device)
+        self._native.check(self._native.load().hb_partials_sum_allreduce(
+            self._handle, ctypes.c_void_p(partials.buffer.data_ptr()), partials.per_plane, partials.n_planes,
+            ctypes.c_void_p(out.data_ptr()), self._native.current_stream_ptr()))
+        return out
+
     def group_sum(self, values, keys, n_groups, out=None):
         """Sum over all ranks of a float32 CUDA vector grouped by a uint8 key -> [n_groups] float64."""
         if out is None:

@@ -300,6 +300,30 @@ int64_t hb_plane_sum_scratch_planes(int32_t device);
 hb_status hb_group_sum(const float* values, const uint8_t* keys, int64_t n, int32_t n_groups,
                        double* out, void* stream);
 
+/* hb_wave_scale that also leaves the first stage of the per-destination totals
+ * (Trace.run_time_ms per destination, analysis/trace.py:26-36) in a buffer of the
+ * caller: partials [D][*per_plane] float64, partials[d * *per_plane + i] = the sum,
+ * NaN results skipped, of one fixed part of destination d's predicted times.
+ * hb_partials_sum (or hb_partials_sum_allreduce across GPUs) turns them into the D
+ * totals.  When the launch takes the table kernel with two records per thread
+ * (every real device row, even K, 8-byte aligned arrays, no dest_regs / status /
+ * limits, D <= 8) each block adds up its own 256 results per destination before
+ * they leave the SM, so the [D x K] plane is not read a second time
+ * (*per_plane = ceil(K / 256)); any other launch runs the first stage of
+ * hb_plane_sum over the results (*per_plane = 256).  Either way a fixed assignment
+ * of records to partial sums and a fixed order: the same inputs give the same bits.
+ * `partials` must hold D * hb_wave_scale_partials_len(K) float64 values; *per_plane
+ * is written on the host before the call returns (0 when K == 0).  Allocates
+ * nothing. */
+int64_t hb_wave_scale_partials_len(int64_t K);
+hb_status hb_wave_scale_partials(const hb_kernel_soa* kernels, int64_t K, int32_t origin_row,
+                                 const int32_t* dest_rows_host, int32_t D, const int16_t* dest_regs,
+                                 const hb_wave_out* out, double* partials, int32_t* per_plane,
+                                 void* stream);
+/* out[p] = sum of partials[p * per_plane .. (p + 1) * per_plane), float64, fixed order. */
+hb_status hb_partials_sum(const double* partials, int32_t per_plane, int32_t n_planes, double* out,
+                          void* stream);
+
 /* hb_plane_sum for callers that must not allocate device memory after start-up
  * (a process that gave the whole GPU to its own memory pool, or one that
  * forbids driver allocations once it is serving).  Same arguments and results
@@ -360,6 +384,9 @@ hb_status hb_plane_sum_allreduce(hb_peer* handle, const float* values, int64_t p
                                  int32_t n_planes, double* out, void* stream);
 hb_status hb_group_sum_allreduce(hb_peer* handle, const float* values, const uint8_t* keys, int64_t n,
                                  int32_t n_groups, double* out, void* stream);
+/* hb_partials_sum whose final stage also exchanges the totals (as above). */
+hb_status hb_partials_sum_allreduce(hb_peer* handle, const double* partials, int32_t per_plane,
+                                    int32_t n_planes, double* out, void* stream);
 /* The exchange alone, in place on n device values.  phase 3 publishes and gathers in
  * one kernel; phases 1 (publish) and 2 (gather what the last publish of every rank
  * left) exist so that several ranks can be walked through one after the other on a

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 import torch
 
-from habitat_b200 import _native, batched, workloads
+from habitat_b200 import _native, batched, device_table, workloads
 from habitat_b200 import distributed as hd
 
 pytestmark = pytest.mark.gpu
@@ -28,6 +28,12 @@ def test_one_rank_equals_the_local_sums():
     for _ in range(3):                                   # both parities of the mailbox
         assert torch.equal(peer.plane_sum(d_p), batched.plane_sum(d_p))
         assert torch.equal(peer.group_sum(d_p[2], d_k, 6), batched.group_sum(d_p[2], d_k, 6))
+    devs = [device_table.load_device_file()[n] for n in workloads.BENCH_DEVICES]
+    kb = batched.KernelBatch.from_numpy(workloads.make_kernels(40000, seed=4))
+    part = batched.WavePartials(40000, 6)
+    for _ in range(2):
+        batched.wave_scale(kb, devs[0], devs, partials=part)
+        assert torch.equal(peer.partials_sum(part), part.totals())
     v = torch.arange(1, 65, dtype=torch.float64, device="cuda")
     assert torch.equal(peer.allreduce_(v.clone()), v)
     with pytest.raises(_native.HabitatNativeError) as err:
@@ -102,6 +108,17 @@ def _worker(rank, world, port, out_dir):
     peer.check_status()
     local = b.plane_sum(d_p).cpu().numpy()
     np.save(os.path.join(out_dir, "rank%d.npy" % rank), np.concatenate([outs[-1][0], outs[-1][1], local]))
+    # totals that the wave-scaling kernel itself starts (this rank's 256-aligned shard of 60,000 kernels)
+    from habitat_b200 import device_table as dt
+    devs = [dt.load_device_file()[n] for n in w.BENCH_DEVICES]
+    kernels = w.make_kernels(60000, seed=12)
+    klo, khi = hdist.shard_bounds_aligned(60000, rank, world, 256)
+    kb = b.KernelBatch.from_numpy({k: v[klo:khi] for k, v in kernels.items()})
+    part = b.WavePartials(khi - klo, 6)
+    b.wave_scale(kb, devs[0], devs, partials=part)
+    fused = peer.partials_sum(part).cpu().numpy()
+    peer.check_status()
+    np.save(os.path.join(out_dir, "fused%d.npy" % rank), fused)
     assert all(np.array_equal(o[0], outs[0][0]) and np.array_equal(o[1], outs[0][1]) for o in outs)
     hdist.host_barrier()
     peer.close()
@@ -124,3 +141,10 @@ def test_two_gpus_exchange_through_ipc(tmp_path):
     keys = g.integers(0, 6, size=50000).astype(np.uint8)
     assert np.allclose(a[:6], planes.astype(np.float64).sum(axis=1), rtol=1e-12)
     assert np.allclose(a[6:12], [planes[1][keys == k].astype(np.float64).sum() for k in range(6)], rtol=1e-12)
+    f0, f1 = np.load(tmp_path / "fused0.npy"), np.load(tmp_path / "fused1.npy")
+    assert np.array_equal(f0, f1)
+    devs = [device_table.load_device_file()[n] for n in workloads.BENCH_DEVICES]
+    kb = batched.KernelBatch.from_numpy(workloads.make_kernels(60000, seed=12))
+    part = batched.WavePartials(60000, 6)
+    batched.wave_scale(kb, devs[0], devs, partials=part)
+    np.testing.assert_allclose(f0, part.totals().cpu().numpy(), rtol=1e-14)

@@ -221,6 +221,70 @@ def test_many_destinations(device_file, D):
     assert_wave_equal(got, run_wave_oracle(kernels, device_file["V100"], dests))
 
 
+def _wave_with_partials(kernels, origin, dests, dest_regs=None, partials=None):
+    kb = batched.KernelBatch.from_numpy(kernels)
+    K, D = len(kb), len(dests)
+    partials = partials or batched.WavePartials(K, D)
+    out = batched.wave_scale(kb, origin, dests, dest_regs=dest_regs, partials=partials)
+    path = batched.wave_scale_path()
+    totals = partials.totals()
+    torch.cuda.synchronize()
+    return out, totals.cpu().numpy(), partials, path
+
+
+@pytest.mark.parametrize("K,D,fused", [(2, 6, True), (254, 1, True), (256, 6, True), (258, 3, True),
+                                       (70000, 6, True), (1 << 20, 6, True), (70001, 6, False), (4096, 9, False)])
+def test_totals_from_the_producing_kernel(bench_devices, device_file, K, D, fused):
+    """wave_scale with `partials`: the table kernel adds up each block's results itself (even K,
+    D <= 8) and any other launch falls back to the first stage of the plane sum; either way the
+    totals are the float64 sums of the predicted times, NaN pairs skipped, and every other output
+    is what the plain call gives."""
+    kernels = workloads.make_kernels(K, seed=K + D)
+    dests = (bench_devices * 2)[:D]
+    out, totals, partials, path = _wave_with_partials(kernels, bench_devices[0], dests)
+    assert path == "wave_scale_lut_kernel"
+    assert partials.per_plane == ((K + 255) // 256 if fused else 256)
+    plain = batched.wave_scale(batched.KernelBatch.from_numpy(kernels), bench_devices[0], dests)
+    for name in ("scaled_ns", "dest_occupancy", "dest_waves", "origin_occupancy", "origin_waves"):
+        a, b = getattr(out, name), getattr(plain, name)
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), name
+    ref = np.nansum(out.scaled_ns.cpu().numpy().astype(np.float64), axis=1)
+    np.testing.assert_allclose(totals, ref, rtol=1e-13)
+    np.testing.assert_allclose(totals, batched.plane_sum(out.scaled_ns).cpu().numpy(), rtol=1e-13)
+    # against the oracle's float64 times: the tolerance of the float32 results
+    oref = run_wave_oracle(kernels, bench_devices[0], dests)
+    want = np.nansum(np.where(oref["status"] < 2, oref["scaled_ns"], np.nan), axis=1)
+    np.testing.assert_allclose(totals, want, rtol=1e-6)
+
+
+def test_totals_partials_edges(bench_devices):
+    # the same bits from call to call, and from a partials object sized for a larger batch
+    kernels = workloads.make_kernels(50000, seed=77)
+    _, t1, p1, _ = _wave_with_partials(kernels, bench_devices[1], bench_devices)
+    _, t2, _, _ = _wave_with_partials(kernels, bench_devices[1], bench_devices, partials=batched.WavePartials(1 << 20, 8))
+    _, t3, _, _ = _wave_with_partials(kernels, bench_devices[1], bench_devices, partials=p1)
+    assert np.array_equal(t1, t2) and np.array_equal(t1, t3)
+    # shards cut on multiples of 256 kernels hold the same blocks: their first-stage sums are the
+    # whole batch's, so the sharded total differs only by the order of the float64 additions
+    parts = []
+    for lo, hi in ((0, 256 * 90), (256 * 90, 50000)):
+        sub = {k: v[lo:hi] for k, v in kernels.items()}
+        parts.append(_wave_with_partials(sub, bench_devices[1], bench_devices)[1])
+    np.testing.assert_allclose(parts[0] + parts[1], t1, rtol=1e-14)
+    # per-destination register counts take the extended kernel: totals through the fallback
+    g = workloads.rng(8)
+    dr = torch.from_numpy(g.integers(-1, 256, size=(6, 50000)).astype(np.int16)).cuda()
+    out, t4, p4, _ = _wave_with_partials(kernels, bench_devices[1], bench_devices, dest_regs=dr)
+    assert p4.per_plane == 256
+    np.testing.assert_allclose(t4, np.nansum(out.scaled_ns.cpu().numpy().astype(np.float64), axis=1), rtol=1e-13)
+    # nothing to do: zero totals
+    _, t0, p0, _ = _wave_with_partials(workloads.make_kernels(0, seed=1), bench_devices[0], bench_devices,
+                                       partials=batched.WavePartials(16, 6))
+    assert p0.per_plane == 0 and np.array_equal(t0, np.zeros(6))
+    with pytest.raises(ValueError):
+        _wave_with_partials(kernels, bench_devices[1], bench_devices, partials=batched.WavePartials(100, 6))
+
+
 def test_plane_sum_scratch_is_kept_per_gpu():
     """The partial sums live in a buffer per GPU that only ever grows and is never freed while a
     launch (or a captured graph) may hold it."""
