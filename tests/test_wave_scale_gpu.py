@@ -347,6 +347,13 @@ for kernels in (_edge_records(bench), workloads.make_kernels(20001, seed=3)):
         assert_wave_equal(got, run_wave_oracle(kernels, bench[0], bench, dest_regs=dr))
     got = run_wave_gpu(kernels, bench[0], bench, metrics=workloads.make_metrics(K, seed=4))
     assert got["fast_path"] == "wave_scale_lut_kernel"
+from habitat_b200 import batched
+kb = batched.KernelBatch.from_numpy(workloads.make_kernels(20000, seed=3))
+part = batched.WavePartials(20000, 6)
+out = batched.wave_scale(kb, bench[0], bench, partials=part)       # the instance that adds up its blocks' results
+assert part.per_plane == 79
+want = np.nansum(out.scaled_ns.cpu().numpy().astype(np.float64), axis=1)
+assert np.allclose(part.totals().cpu().numpy(), want, rtol=1e-13)
 assert lib.hb_bounds_check_word(ctypes.byref(word), 0) == 0
 assert word.value == 0, hex(word.value)
 print("checked build ok")
