@@ -1098,6 +1098,9 @@ def main():
                      "us_per_launch": kern_us, "kernels_per_launch": sw.khi - sw.klo,
                      "algorithmic_bytes_per_pair": WAVE_BYTES_PER_PAIR,
                      "timing": "CUDA events around the kernel inside the timed steps (rank 0)",
+                     "instance": "the one whose blocks also add up their own results per destination (11 % more "
+                                 "instructions than the plain instance timed under config2; in exchange no second "
+                                 "pass over the predicted times)",
                      "traffic": None},
         "e2e": {"value": pairs_total / (e2e["wave_ms"] * 1e-3), "unit": "pairs/s",
                 "h2d_bytes_per_step": workloads.SWEEP_KERNELS * 20, "d2h_bytes_per_step": pairs_total * 4,
