@@ -5,9 +5,11 @@ One JSON line on stdout (rank 0).  A step is one pass over the whole batch: 67,1
 (kernel x destination) pairs of wave scaling (11,184,812 kernels to six device rows) plus
 16,777,216 MLP queries (4,194,304 for each of the conv2d, linear, bmm and lstm predictors).
 Under torchrun (one rank per GPU) the batch is sharded: every rank takes a contiguous range of
-kernels and of each predictor's queries, and each step ends its two phases with one NCCL
-all-reduce of the per-destination totals ([6] for the pairs, [4 x 6] for the queries), inside
-the timed region.  The same command on one GPU runs the whole batch (strong scaling).
+kernels and of each predictor's queries, and each step ends its two phases with the all-reduce
+of the per-destination totals ([6] for the pairs, [4 x 6] for the queries) inside the timed
+region: by default inside the final stage of the reductions, through mailboxes in the peer GPUs'
+memory (`--totals nccl`: NCCL all-reduces).  The same command on one GPU runs the whole batch
+(strong scaling).
 
 The headline `value` is wave-scaled pairs per second over the wave-scaling phases of the timed
 steps; the `mlp` object carries predictions per second over the MLP phases.  Both are measured
