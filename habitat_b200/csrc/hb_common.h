@@ -100,5 +100,34 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
   cfg.numAttrs = overlapped_launch_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// The same with the grid's blocks grouped into thread-block clusters of `cluster_x` consecutive
+// blocks (grid.x must be a multiple of it); cluster_x == 1 is the plain launch above.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, unsigned cluster_x,
+                                             cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (overlapped_launch_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 }  // namespace hb
 #endif

@@ -109,16 +109,19 @@ __device__ __forceinline__ double peer_collect(const PeerView& pv, int i, double
 // Final stage + exchange: block i adds the `per_plane` partial sums of value i, publishes the result
 // to every rank and gathers the ranks' results.  phase: 1 publish only, 2 gather only (of a
 // value published by an earlier launch: `out` holds it), 3 both (the normal, fused call).
+// CLUSTER consecutive blocks share a value when its list of partial sums is long (the launch
+// then carries that cluster dimension); the first of them does the exchange.
+template <int CLUSTER>
 __global__ void __launch_bounds__(kFinalThreadsMax)
 peer_final_exchange_kernel(const double* __restrict__ partial, int per_plane, double* __restrict__ out,
                            const PeerView pv, int phase) {
   hb_grid_dependency_wait();
   __shared__ double sh[kPeerMaxWorld];
-  const int i = blockIdx.x;
+  const int i = blockIdx.x / CLUSTER;
   double mine = 0.0;
   if (phase & 1) {
-    const double v = partial ? partials_share(partial + static_cast<size_t>(i) * per_plane, per_plane) : 0.0;
-    const double t = block_sum(v);
+    const double t = partial ? plane_total<CLUSTER>(partial, per_plane) : 0.0;
+    if (CLUSTER > 1 && blockIdx.x % CLUSTER != 0) return;   // helped with the sum; past the cluster's last barrier
     if (threadIdx.x == 0) sh[0] = partial ? t : out[i];
     __syncthreads();
     mine = sh[0];
@@ -306,7 +309,7 @@ extern "C" hb_status hb_plane_sum_allreduce(hb_peer* h, const float* values, int
   ++h->seq;
   HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(n_planes, kPlaneBlocks), dim3(kSumThreads), 0, s,
                                     values, plane_len, h->partial));
-  HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n_planes), dim3(kSumThreads), 0, s,
+  HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel<1>, dim3(n_planes), dim3(kSumThreads), 0, s,
                                     static_cast<const double*>(h->partial), kPlaneBlocks, out, view_of(h), 3));
   return HB_OK;
 }
@@ -321,9 +324,15 @@ extern "C" hb_status hb_partials_sum_allreduce(hb_peer* h, const double* partial
   if (st != HB_OK) return st;
   ++h->seq;
   // an empty shard (per_plane 0) still takes part in the exchange, with zeros
-  HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n_planes), dim3(final_threads(per_plane)), 0,
-                                    static_cast<cudaStream_t>(stream), per_plane > 0 ? partials : h->partial, per_plane,
-                                    out, view_of(h), 3));
+  const double* list = per_plane > 0 ? partials : h->partial;
+  if (final_cluster(per_plane) == 1) {
+    HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel<1>, dim3(n_planes), dim3(final_threads(per_plane)), 0,
+                                      static_cast<cudaStream_t>(stream), list, per_plane, out, view_of(h), 3));
+  } else {
+    HB_CUDA_TRY(hb::launch_overlapped_cluster(peer_final_exchange_kernel<kFinalCluster>,
+                                              dim3(n_planes * kFinalCluster), dim3(kFinalThreadsMax), kFinalCluster,
+                                              static_cast<cudaStream_t>(stream), list, per_plane, out, view_of(h), 3));
+  }
   return HB_OK;
 }
 
@@ -339,7 +348,7 @@ extern "C" hb_status hb_group_sum_allreduce(hb_peer* h, const float* values, con
   ++h->seq;
   HB_CUDA_TRY(hb::launch_overlapped(group_partial_kernel, dim3(kGroupBlocks), dim3(kSumThreads), 0, s, values,
                                     keys, n, 0, n_groups, h->partial));
-  HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n_groups), dim3(kSumThreads), 0, s,
+  HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel<1>, dim3(n_groups), dim3(kSumThreads), 0, s,
                                     static_cast<const double*>(h->partial), kGroupBlocks, out, view_of(h), 3));
   return HB_OK;
 }
@@ -353,7 +362,7 @@ extern "C" hb_status hb_peer_allreduce(hb_peer* h, double* values, int32_t n, in
   if (st != HB_OK) return st;
   if (phase & 1) ++h->seq;      // a gather-only call belongs to the publish before it
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel, dim3(n), dim3(kSumThreads), 0, s,
+  HB_CUDA_TRY(hb::launch_overlapped(peer_final_exchange_kernel<1>, dim3(n), dim3(kSumThreads), 0, s,
                                     static_cast<const double*>(nullptr), 0, values, view_of(h), phase));
   return HB_OK;
 }

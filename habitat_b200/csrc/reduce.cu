@@ -30,13 +30,12 @@ segment_sum_kernel(const float* __restrict__ values, const int64_t* __restrict__
   }
 }
 
+template <int CLUSTER>
 __global__ void __launch_bounds__(kFinalThreadsMax)
 plane_final_kernel(const double* __restrict__ partial, int per_plane, double* __restrict__ out) {
   hb_grid_dependency_wait();
-  const int plane = blockIdx.x;
-  const double v = partials_share(partial + static_cast<size_t>(plane) * per_plane, per_plane);
-  const double t = block_sum(v);
-  if (threadIdx.x == 0) out[plane] = t;
+  const double t = plane_total<CLUSTER>(partial, per_plane);
+  if (threadIdx.x == 0 && blockIdx.x % CLUSTER == 0) out[blockIdx.x / CLUSTER] = t;
 }
 
 __global__ void __launch_bounds__(256)
@@ -134,7 +133,7 @@ extern "C" hb_status hb_plane_sum(const float* values, int64_t plane_len, int32_
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   HB_CUDA_TRY(hb::launch_overlapped(plane_partial_kernel, dim3(n_planes, kPlaneBlocks), dim3(kSumThreads), 0, s,
                                     values, plane_len, sc.plane));
-  HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel, dim3(n_planes), dim3(kSumThreads), 0, s,
+  HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel<1>, dim3(n_planes), dim3(kSumThreads), 0, s,
                                     static_cast<const double*>(sc.plane), kPlaneBlocks, out));
   return HB_OK;
 }
@@ -146,8 +145,14 @@ extern "C" hb_status hb_partials_sum(const double* partials, int32_t per_plane, 
     return HB_ERR_INVALID_ARGUMENT;
   }
   if (n_planes == 0) return HB_OK;
-  HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel, dim3(n_planes), dim3(final_threads(per_plane)), 0,
-                                    static_cast<cudaStream_t>(stream), partials, per_plane, out));
+  if (final_cluster(per_plane) == 1) {
+    HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel<1>, dim3(n_planes), dim3(final_threads(per_plane)), 0,
+                                      static_cast<cudaStream_t>(stream), partials, per_plane, out));
+  } else {
+    HB_CUDA_TRY(hb::launch_overlapped_cluster(plane_final_kernel<kFinalCluster>, dim3(n_planes * kFinalCluster),
+                                              dim3(kFinalThreadsMax), kFinalCluster,
+                                              static_cast<cudaStream_t>(stream), partials, per_plane, out));
+  }
   return HB_OK;
 }
 
@@ -168,7 +173,7 @@ extern "C" hb_status hb_group_sum(const float* values, const uint8_t* keys, int6
     HB_CUDA_TRY(hb::launch_overlapped(group_partial_kernel, dim3(kGroupBlocks), dim3(kSumThreads), 0, s, values,
                                       keys, n, g0, ng, sc.group));
     static_assert(kGroupBlocks == kPlaneBlocks, "the final stage is shared with the plane sum");
-    HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel, dim3(ng), dim3(kSumThreads), 0, s,
+    HB_CUDA_TRY(hb::launch_overlapped(plane_final_kernel<1>, dim3(ng), dim3(kSumThreads), 0, s,
                                       static_cast<const double*>(sc.group), kGroupBlocks, out + g0));
   }
   return HB_OK;
@@ -241,7 +246,7 @@ extern "C" hb_status hb_plane_sum_static(const float* values, int64_t plane_len,
   // has to start at zero; whatever the previous call left there is overwritten.
   plane_partial_kernel<<<dim3(n_planes, kPlaneBlocks), kSumThreads, 0, s>>>(values, plane_len, scratch);
   HB_CUDA_TRY(cudaGetLastError());
-  plane_final_kernel<<<n_planes, kSumThreads, 0, s>>>(scratch, kPlaneBlocks, out);
+  plane_final_kernel<1><<<n_planes, kSumThreads, 0, s>>>(scratch, kPlaneBlocks, out);
   HB_CUDA_TRY(cudaGetLastError());
   return HB_OK;
 }

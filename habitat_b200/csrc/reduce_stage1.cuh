@@ -4,6 +4,8 @@
 // result does not depend on scheduling (no floating-point atomics) and is the same bits in both files.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "hb_common.h"
 
 namespace {
@@ -59,9 +61,39 @@ __device__ __forceinline__ double partials_share(const double* __restrict__ q, i
 
 // Threads per block of a final stage over `per_plane` first-stage sums: the plane sums' own 256
 // first-stage sums keep the block size their results were defined with; long lists (one sum per
-// block of the wave-scaling kernel) get 1024 threads so that more loads are in flight.
+// block of the wave-scaling kernel) get 1024 threads so that more loads are in flight, and very
+// long ones a cluster of blocks per plane, each block adding one contiguous part of the list.
 constexpr int kFinalThreadsMax = 1024;
+constexpr int kFinalCluster = 8;
 inline int final_threads(int per_plane) { return per_plane > 2 * kSumThreads ? kFinalThreadsMax : kSumThreads; }
+inline int final_cluster(int per_plane) { return per_plane > 8 * kFinalThreadsMax ? kFinalCluster : 1; }
+
+// Sum of the `per_plane` first-stage sums of plane blockIdx.x / CLUSTER, formed by the CLUSTER
+// consecutive blocks that share the plane; valid in thread 0 of the first of them.  With
+// CLUSTER > 1 the kernel must have been launched with that cluster dimension: block r adds part r
+// of the list, stores its sum into slot r of the first block's shared memory, and the first block
+// adds the slots in order, so the result is fixed by (per_plane, block size, CLUSTER).  The
+// one-block form is an instantiation of its own: kernels that contain cluster code launched
+// measurably slower (≈ 0.8 µs) even when they were not launched as clusters.
+template <int CLUSTER>
+__device__ __forceinline__ double plane_total(const double* __restrict__ partial, int per_plane) {
+  constexpr int cluster = CLUSTER;
+  const int plane = blockIdx.x / cluster, r = blockIdx.x % cluster;
+  const int part = (per_plane + cluster - 1) / cluster;
+  const int lo = r * part < per_plane ? r * part : per_plane;
+  const int hi = lo + part < per_plane ? lo + part : per_plane;
+  const double t = block_sum(partials_share(partial + static_cast<size_t>(plane) * per_plane + lo, hi - lo));
+  if (cluster == 1) return t;
+  __shared__ double slots[kFinalCluster];
+  cooperative_groups::cluster_group c = cooperative_groups::this_cluster();
+  c.sync();                                   // every block of the cluster runs: its shared memory may be written
+  if (threadIdx.x == 0) c.map_shared_rank(slots, 0)[r] = t;
+  c.sync();                                   // the slots are visible to the first block
+  double total = 0.0;
+  if (r == 0 && threadIdx.x == 0)
+    for (int q = 0; q < cluster; ++q) total += slots[q];
+  return total;
+}
 
 // Stage 1 of the plane sum: a fixed number of blocks per plane, each summing a
 // fixed contiguous chunk; NaN entries (pairs the reference raises on) skipped.

@@ -29,11 +29,12 @@ def test_one_rank_equals_the_local_sums():
         assert torch.equal(peer.plane_sum(d_p), batched.plane_sum(d_p))
         assert torch.equal(peer.group_sum(d_p[2], d_k, 6), batched.group_sum(d_p[2], d_k, 6))
     devs = [device_table.load_device_file()[n] for n in workloads.BENCH_DEVICES]
-    kb = batched.KernelBatch.from_numpy(workloads.make_kernels(40000, seed=4))
-    part = batched.WavePartials(40000, 6)
-    for _ in range(2):
-        batched.wave_scale(kb, devs[0], devs, partials=part)
-        assert torch.equal(peer.partials_sum(part), part.totals())
+    for n_kernels in (40000, 2200000):                   # the longer list takes a cluster of blocks per value
+        kb = batched.KernelBatch.from_numpy(workloads.make_kernels(n_kernels, seed=4))
+        part = batched.WavePartials(n_kernels, 6)
+        for _ in range(2):
+            batched.wave_scale(kb, devs[0], devs, partials=part)
+            assert torch.equal(peer.partials_sum(part), part.totals())
     v = torch.arange(1, 65, dtype=torch.float64, device="cuda")
     assert torch.equal(peer.allreduce_(v.clone()), v)
     with pytest.raises(_native.HabitatNativeError) as err:

@@ -233,12 +233,14 @@ def _wave_with_partials(kernels, origin, dests, dest_regs=None, partials=None):
 
 
 @pytest.mark.parametrize("K,D,fused", [(2, 6, True), (254, 1, True), (256, 6, True), (258, 3, True),
-                                       (70000, 6, True), (1 << 20, 6, True), (70001, 6, False), (4096, 9, False)])
+                                       (70000, 6, True), (1 << 20, 6, True), (2500000, 6, True), (70001, 6, False),
+                                       (4096, 9, False)])
 def test_totals_from_the_producing_kernel(bench_devices, device_file, K, D, fused):
     """wave_scale with `partials`: the table kernel adds up each block's results itself (even K,
     D <= 8) and any other launch falls back to the first stage of the plane sum; either way the
     totals are the float64 sums of the predicted times, NaN pairs skipped, and every other output
-    is what the plain call gives."""
+    is what the plain call gives.  (2,500,000 kernels leave 9,766 sums per destination: the final
+    stage then spreads a destination over a cluster of blocks.)"""
     kernels = workloads.make_kernels(K, seed=K + D)
     dests = (bench_devices * 2)[:D]
     out, totals, partials, path = _wave_with_partials(kernels, bench_devices[0], dests)
