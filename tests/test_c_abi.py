@@ -53,3 +53,18 @@ def test_struct_layouts_match_the_header():
     fields = re.search(r"typedef struct \{(.*?)\} hb_device_spec;", text, flags=re.S).group(1)
     names = re.findall(r"int32_t\s+(\w+);", fields)
     assert tuple(names) == _native.DEVICE_SPEC_FIELDS
+
+
+def test_partials_buffer_size_and_argument_checks():
+    """Host-only parts of the totals entry points: the buffer size per destination (one sum per
+    256 kernels, never fewer than the 256 sums of the fallback) and the refusal of bad arguments
+    before anything touches a GPU."""
+    lib = _native.load()
+    sizes = {0: 256, 1: 256, 65536: 256, 65538: 257, 1 << 20: 4096, 11184812: 43691}
+    for k, want in sizes.items():
+        assert lib.hb_wave_scale_partials_len(k) == want
+    assert lib.hb_wave_scale_partials_len(-1) == -1
+    assert lib.hb_partials_sum(None, 4, 2, None, None) == _native.HB_ERR_INVALID_ARGUMENT
+    assert lib.hb_partials_sum(None, -1, 0, None, None) == _native.HB_ERR_INVALID_ARGUMENT
+    assert lib.hb_partials_sum(None, 0, 0, None, None) == 0          # nothing to do
+    assert b"hb_partials_sum" in lib.hb_last_error()
