@@ -742,7 +742,50 @@ def e2e_sweep(ctx, sw):
         copy = {"h2d_gbs_per_rank": ctx.reduce(reps * pipe.h2d_bytes / (c0.elapsed_time(c1) * 1e-3) / 1e9, "min"),
                 "d2h_gbs_per_rank": ctx.reduce(reps * pipe.d2h_bytes / (c1.elapsed_time(c2) * 1e-3) / 1e9, "min"),
                 "ranks_copying_at_once": ctx.world}
-    del pipe, pipe_rest, blocks
+    # the same pass for a caller that only wants the per-destination totals of every chunk back
+    # (Trace.run_time_ms per destination): 8 x 6 bytes down per chunk instead of 4 bytes per pair
+    t_pipe = hostio.WaveScaleHost(ctx.origin, ctx.bench_devs, E2E_CHUNK_K, depth=depth, results=("totals",)) if full else None
+    t_rest = hostio.WaveScaleHost(ctx.origin, ctx.bench_devs, rest[1] - rest[0], depth=1, results=("totals",)) if rest else None
+
+    def totals_pass(e_end=None, gather=None):
+        for i in range(len(full)):
+            if gather is not None:
+                t_pipe.wait(i % depth)
+                if i >= depth:
+                    gather += t_pipe.host_out[i % depth]["totals"].numpy()
+            t_pipe.submit(blocks[i], i % depth)
+        if rest:
+            t_rest.submit(blocks[-1], 0)
+        if gather is not None:
+            for i in range(max(0, len(full) - depth), len(full)):
+                t_pipe.wait(i % depth)
+                gather += t_pipe.host_out[i % depth]["totals"].numpy()
+            if rest:
+                t_rest.wait(0)
+                gather += t_rest.host_out[0]["totals"].numpy()
+        if e_end is not None:
+            if full:
+                join.wait_event(t_pipe.downloaded[(len(full) - 1) % depth])
+            if rest:
+                join.wait_event(t_rest.downloaded[0])
+            e_end.record(join)
+    chunk_totals = np.zeros(WAVE_D)
+    totals_pass(gather=chunk_totals)
+    with torch.cuda.stream(ctx.stream):
+        from habitat_b200 import batched
+        batched.wave_scale(sw.kb, ctx.origin, ctx.bench_devs, out=sw.out, partials=sw.partials)
+        shard_totals = sw.partials.totals().cpu().numpy()
+    totals_rel = float(np.max(np.abs(chunk_totals - shard_totals) / np.abs(shard_totals))) if n else 0.0
+    ctx.barrier()
+    t0, t1 = ctx.event(), ctx.event()
+    t0.record((t_pipe or t_rest).s_up)
+    for p in range(passes):
+        totals_pass(t1 if p == passes - 1 else None)
+    ctx.barrier()
+    totals_ms = ctx.reduce(t0.elapsed_time(t1)) / passes
+    totals_rel = ctx.reduce(totals_rel)
+    ctx.launches += (passes + 1) * 2 * len(chunks) + 2
+    del pipe, pipe_rest, t_pipe, t_rest, blocks
 
     nq = sw.qhi - sw.qlo
     qchunks = [(a, min(a + E2E_CHUNK_Q, nq)) for a in range(0, nq, E2E_CHUNK_Q)]
@@ -775,7 +818,8 @@ def e2e_sweep(ctx, sw):
         h.check_status()
     h2d_q = sum(sw.host_q[op][0].nbytes + sw.host_q[op][1].nbytes for op in sw.ops)
     return {"wave_ms": wave_ms, "mlp_ms": mlp_ms, "wave_h2d": n * hostio.RECORD_BYTES, "wave_d2h": n * WAVE_D * 4,
-            "mlp_h2d": h2d_q, "mlp_d2h": nq * 4 * len(sw.ops), "copy": copy}
+            "mlp_h2d": h2d_q, "mlp_d2h": nq * 4 * len(sw.ops), "copy": copy,
+            "totals_ms": totals_ms, "totals_d2h": len(chunks) * WAVE_D * 8, "totals_rel": totals_rel}
 
 
 def config4(ctx, handles, cpu_leg):
@@ -1106,7 +1150,14 @@ def main():
                      "traffic": None},
         "e2e": {"value": pairs_total / (e2e["wave_ms"] * 1e-3), "unit": "pairs/s",
                 "h2d_bytes_per_step": workloads.SWEEP_KERNELS * 20, "d2h_bytes_per_step": pairs_total * 4,
-                "copy_rates": e2e["copy"]},
+                "copy_rates": e2e["copy"],
+                "totals_only": {"value": pairs_total / (e2e["totals_ms"] * 1e-3), "unit": "pairs/s",
+                                "what": "the same pass for a caller that wants only the per-destination totals of "
+                                        "each chunk back (the kernel's blocks add up their own results; nothing "
+                                        "else is downloaded)",
+                                "h2d_bytes_per_step": workloads.SWEEP_KERNELS * 20,
+                                "d2h_bytes_per_step_per_rank": e2e["totals_d2h"],
+                                "chunk_totals_vs_device_totals_max_rel_diff": e2e["totals_rel"]}},
         "totals_identical_every_step": same_every_step,
     }
     mlp = {

@@ -111,15 +111,23 @@ class WaveScaleHost(_Streams):
     submit(block, slot): `block` is a pinned uint8 tensor from pack_kernels (K * 20 bytes).
     The outputs listed in `results` appear in self.host_out[slot] (pinned tensors, same names
     as batched.WaveResult); the predicted times are what the analyzer's path returns per
-    kernel, the other outputs stay on the device (self.dev_out[slot]) unless listed."""
+    kernel, the other outputs stay on the device (self.dev_out[slot]) unless listed.
+    "totals" asks for the [D] float64 per-destination sums of the batch's predicted times (what
+    Trace.run_time_ms is per destination): the kernel's blocks add up their own results, so a
+    caller that only wants totals (results=("totals",)) downloads 8 D bytes per batch."""
 
     def __init__(self, origin, dests: Sequence, K: int, depth: int = 3, results: Sequence[str] = ("scaled_ns",)):
         super().__init__(depth)
-        unknown = [r for r in results if r not in _WAVE_OUT]
+        unknown = [r for r in results if r not in _WAVE_OUT + ("totals",)]
         if unknown:
             raise ValueError("unknown wave-scaling outputs: %s" % unknown)
         self.origin, self.dests, self.K = origin, list(dests), K
         D = len(self.dests)
+        self.want_totals = "totals" in results
+        results = [r for r in results if r != "totals"]
+        if self.want_totals:
+            self.partials = [batched.WavePartials(K, D) for _ in range(depth)]
+            self.dev_totals = [torch.zeros((D,), dtype=torch.float64, device="cuda") for _ in range(depth)]
         self.dev_block = [torch.empty((K * RECORD_BYTES,), dtype=torch.uint8, device="cuda") for _ in range(depth)]
         self.dev_in = [batched.KernelBatch(**_views(b, K)) for b in self.dev_block]
         self.dev_out = []
@@ -133,6 +141,9 @@ class WaveScaleHost(_Streams):
         with numa_local(torch.cuda.current_device()):
             self.host_out = [{k: torch.empty_like(getattr(o, k), device="cpu").pin_memory() for k in results}
                              for o in self.dev_out]
+            if self.want_totals:
+                for h in self.host_out:
+                    h["totals"] = torch.zeros((D,), dtype=torch.float64).pin_memory()
         self.h2d_bytes = K * RECORD_BYTES
         self.d2h_bytes = sum(t.numel() * t.element_size() for t in self.host_out[0].values())
 
@@ -150,12 +161,17 @@ class WaveScaleHost(_Streams):
             # the kernel of this batch overwrites outputs the download of batch (i - depth) reads
             if self.used[slot]:
                 self.s_in.wait_event(self.downloaded[slot])
-            batched.wave_scale(self.dev_in[slot], self.origin, self.dests, out=self.dev_out[slot])
+            if self.want_totals:
+                batched.wave_scale(self.dev_in[slot], self.origin, self.dests, out=self.dev_out[slot],
+                                   partials=self.partials[slot])
+                self.partials[slot].totals(out=self.dev_totals[slot])
+            else:
+                batched.wave_scale(self.dev_in[slot], self.origin, self.dests, out=self.dev_out[slot])
             self.computed[slot].record(self.s_in)
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_event(self.computed[slot])
             for k, t in self.host_out[slot].items():
-                t.copy_(getattr(self.dev_out[slot], k), non_blocking=True)
+                t.copy_(self.dev_totals[slot] if k == "totals" else getattr(self.dev_out[slot], k), non_blocking=True)
             self.downloaded[slot].record(self.s_out)
         self.used[slot] = True
 

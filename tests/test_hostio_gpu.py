@@ -43,6 +43,18 @@ def test_wave_scale_pipeline(bench_devices):
     assert list(times.host_out[0]) == ["scaled_ns"] and times.d2h_bytes == 4 * 6 * K
     assert np.isnan(got[~ok]).all() and (np.abs(got[ok] - ref["scaled_ns"][ok]) <= 1e-6 * ref["scaled_ns"][ok]).all()
     assert np.array_equal(to_numpy(times.dev_out[0].dest_occupancy), ref["dest_occupancy"])
+    # totals only: the per-destination sums of a batch come back, nothing else is downloaded
+    sums = hostio.WaveScaleHost(bench_devices[0], bench_devices, K, depth=2, results=("totals",))
+    for i in range(3):
+        sums.wait(i % 2)
+        sums.submit(blocks[i], i % 2)
+    sums.wait(0)
+    ref2 = run_wave_oracle(batches[2], bench_devices[0], bench_devices)
+    want = np.where(ref2["status"] <= 1, ref2["scaled_ns"], 0.0).sum(axis=1)
+    assert list(sums.host_out[0]) == ["totals"] and sums.d2h_bytes == 8 * 6
+    np.testing.assert_allclose(to_numpy(sums.host_out[0]["totals"]), want, rtol=1e-6)
+    np.testing.assert_allclose(to_numpy(sums.host_out[0]["totals"]),
+                               np.nansum(to_numpy(sums.dev_out[0].scaled_ns).astype(np.float64), axis=1), rtol=1e-13)
     with pytest.raises(ValueError):
         hostio.WaveScaleHost(bench_devices[0], bench_devices, K, results=("scaled",))
     with pytest.raises(ValueError):
