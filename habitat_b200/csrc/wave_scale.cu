@@ -487,21 +487,22 @@ __device__ __forceinline__ void store_byte_pair(uint8_t* q, uint32_t pair_word, 
 
 // TOT: every block also adds up its own results per destination (float64, fixed order, NaN results
 // skipped like the plane sums do) and leaves the sums in p.block_sums[d * gridDim.x + block], so
-// the totals of a launch need no second pass over the [D x K] plane.  A thread parks its two
-// results per destination in shared memory; at the end sixteen lanes per destination add the
-// block's 256 values.  Needs a grid that covers the batch in one pass and D <= kTotMaxD.
+// the totals of a launch need no second pass over the [D x K] plane.  A thread parks the float64
+// sum of its two results per destination in shared memory; at the end sixteen lanes per
+// destination add the block's 128 sums.  Needs a grid that covers the batch in one pass and
+// D <= kTotMaxD.
 constexpr int kTotMaxD = kLutThreads / 16;
 
 template <int VEC, bool EXT, bool ALIGNED, int NP, int NS, bool TOT = false>
 __global__ void __launch_bounds__(kLutThreads, EXT ? 8 : 12)
 wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
   static_assert(!TOT || (VEC == 2 && ALIGNED && !EXT), "fused totals: aligned two-record variant only");
-  __shared__ float2 s_tot[TOT ? kTotMaxD : 1][TOT ? kLutThreads : 1];
+  __shared__ double s_tot[TOT ? kTotMaxD : 1][TOT ? kLutThreads : 1];
   hb_grid_dependency_wait();
   const uint32_t K = lp.K;
   const int D = lp.D;
   if (TOT && (blockIdx.x * kLutThreads + threadIdx.x) * VEC >= K) {
-    for (int d = 0; d < D; ++d) s_tot[d][threadIdx.x] = make_float2(0.0f, 0.0f);   // threads past the end
+    for (int d = 0; d < D; ++d) s_tot[d][threadIdx.x] = 0.0;   // threads past the end
   }
   const uint8_t* __restrict__ tab_t = reinterpret_cast<const uint8_t*>(g_lut_t);
   const uint32_t stride = gridDim.x * (kLutThreads * VEC);
@@ -670,7 +671,11 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
       store_pair<uint32_t, VEC, ALIGNED>(p.dest_waves + base, wavv, pair);
       store_byte_pair<VEC, ALIGNED>(p.dest_occ + base, occ2, pair);
       if (with_status) store_byte_pair<VEC, ALIGNED>(p.status + base, st2, pair);
-      if (TOT) s_tot[d][threadIdx.x] = make_float2(outv.v[0], outv.v[VEC - 1]);
+      if (TOT) {
+        const float g0 = outv.v[0] == outv.v[0] ? outv.v[0] : 0.0f;                     // NaN: no prediction
+        const float g1 = outv.v[VEC - 1] == outv.v[VEC - 1] ? outv.v[VEC - 1] : 0.0f;
+        s_tot[d][threadIdx.x] = static_cast<double>(g0) + static_cast<double>(g1);   // exact
+      }
     }
   }
   if (TOT) {
@@ -678,15 +683,11 @@ wave_scale_lut_kernel(const Ptrs p, const __grid_constant__ LutParams lp) {
     const int d = threadIdx.x >> 4, j = threadIdx.x & 15;
     double acc = 0.0;
     if (d < D) {
-      const float4* row = reinterpret_cast<const float4*>(s_tot[d]);
+      const double2* row = reinterpret_cast<const double2*>(s_tot[d]);
 #pragma unroll
       for (int i = 0; i < kLutThreads / 32; ++i) {
-        const float4 x = row[j + 16 * i];
-        const double a0 = static_cast<double>(x.x == x.x ? x.x : 0.0f);   // NaN: no prediction for the pair
-        const double a1 = static_cast<double>(x.y == x.y ? x.y : 0.0f);
-        const double a2 = static_cast<double>(x.z == x.z ? x.z : 0.0f);
-        const double a3 = static_cast<double>(x.w == x.w ? x.w : 0.0f);
-        acc += (a0 + a1) + (a2 + a3);
+        const double2 x = row[j + 16 * i];
+        acc += x.x + x.y;
       }
     }
 #pragma unroll
