@@ -38,7 +38,9 @@ __device__ __forceinline__ double block_sum(double v) {
 // fixed assignment for a given block size, so the value does not depend on scheduling).  With
 // per_plane <= blockDim.x it is the thread's own element.
 __device__ __forceinline__ double partials_share(const double* __restrict__ q, int per_plane) {
-  constexpr int kWays = 8;   // sixteen measured slower: accumulators and loads in flight no longer fit the registers of a 1024-thread block
+  // eight ways: sixteen measured slower (accumulators plus loads in flight no longer fit the
+  // 64 registers a thread of a 1024-thread block may have)
+  constexpr int kWays = 8;
   double a[kWays];
 #pragma unroll
   for (int u = 0; u < kWays; ++u) a[u] = 0.0;
