@@ -455,6 +455,34 @@ def case_config2_totals(ctx):
     return {"workload": "per-destination totals of the predicted times, 6 device rows", "launch_sizes": rows}
 
 
+def case_sweep_kernel(ctx):
+    """The default run's own wave-scaling launch alone: the table kernel with block sums on the
+    sweep's 11,184,812 kernels, two buffer sets (1.7 GB, so no launch finds its data in L2), two
+    warm-up and six timed launches.  A small command for profilers."""
+    torch = ctx.torch
+    from habitat_b200 import batched, workloads
+    K = workloads.SWEEP_KERNELS
+    with torch.cuda.stream(ctx.stream):
+        kbs = [batched.KernelBatch.from_numpy(workloads.sweep_kernels(0, K)),
+               batched.KernelBatch.from_numpy(workloads.make_kernels(K, 4242))]
+        parts = [batched.WavePartials(K, WAVE_D) for _ in range(2)]
+        outs = [batched.wave_scale(kbs[q], ctx.origin, ctx.bench_devs, partials=parts[q]) for q in range(2)]
+        torch.cuda.synchronize()
+        e0, e1 = ctx.event(), ctx.event()
+        e0.record(ctx.stream)
+        for i in range(6):
+            batched.wave_scale(kbs[i % 2], ctx.origin, ctx.bench_devs, out=outs[i % 2], partials=parts[i % 2])
+        e1.record(ctx.stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / 6
+        ctx.launches += 8
+    gbs = K * WAVE_D * WAVE_BYTES_PER_PAIR / (us * 1e-6) / 1e9
+    return {"workload": "the sweep's wave-scaling launch alone (11,184,812 kernels x 6 device rows, block sums)",
+            "kernel": batched.wave_scale_path(), "kernels": K, "first_stage_sums_per_destination": parts[0].per_plane,
+            "us_per_launch": us, "achieved": gbs, "peak": ctx.peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": gbs / ctx.peaks["hbm_gbs"], "launches_timed": 6}
+
+
 def case_config3(ctx):
     """Kernel-only timing of configuration 3: conv2d predictor, 262,144 queries, bf16."""
     torch = ctx.torch
@@ -1004,7 +1032,7 @@ def main():
     ap.add_argument("--totals", default="peer", choices=["peer", "nccl"],
                     help="how the per-step totals are summed across GPUs")
     ap.add_argument("--case", default="all",
-                    choices=["all", "config2", "config2-large", "config2-totals", "config2-status", "config2-regs", "config2-metrics",
+                    choices=["all", "config2", "config2-large", "config2-totals", "sweep-kernel", "config2-status", "config2-regs", "config2-metrics",
                              "config3", "config1"],
                     help="run one kernel-only sub-entry alone and print it (for profilers)")
     args = ap.parse_args()
@@ -1020,6 +1048,7 @@ def main():
             fn = {"config2": lambda: case_config2(ctx, large=False),
                   "config2-large": lambda: case_config2(ctx, small=False),
                   "config2-totals": lambda: case_config2_totals(ctx),
+                  "sweep-kernel": lambda: case_sweep_kernel(ctx),
                   "config2-status": lambda: case_config2_inputs(ctx, "status"),
                   "config2-regs": lambda: case_config2_inputs(ctx, "regs"),
                   "config2-metrics": lambda: case_config2_inputs(ctx, "metrics"),
