@@ -16,7 +16,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_shard_bounds_cover_everything():
     for n in (0, 1, 5, 64, 1000, 1 << 20, (1 << 20) + 3):
         for world in (1, 2, 3, 4, 8):
-            for fn in (hd.shard_bounds, lambda a, b, c: hd.shard_bounds_aligned(a, b, c, 4)):
+            for fn in (hd.shard_bounds, lambda a, b, c: hd.shard_bounds_aligned(a, b, c, 4),
+                       lambda a, b, c: hd.shard_bounds_aligned(a, b, c, 256)):   # the benchmark's kernel shards
                 edges = [fn(n, r, world) for r in range(world)]
                 assert edges[0][0] == 0 and edges[-1][1] == n
                 assert all(a[1] == b[0] for a, b in zip(edges, edges[1:]))
@@ -24,8 +25,9 @@ def test_shard_bounds_cover_everything():
             sizes = [hi - lo for lo, hi in (hd.shard_bounds(n, r, world) for r in range(world))]
             assert max(sizes) - min(sizes) <= 1
             for r in range(world - 1):
-                assert hd.shard_bounds_aligned(n, r, world, 4)[1] % 4 == 0 or \
-                    hd.shard_bounds_aligned(n, r, world, 4)[1] == n
+                for align in (4, 256):
+                    assert hd.shard_bounds_aligned(n, r, world, align)[1] % align == 0 or \
+                        hd.shard_bounds_aligned(n, r, world, align)[1] == n
 
 
 def _worker(rank, world, port, n, out_dir):
