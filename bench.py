@@ -43,6 +43,7 @@ WAVE_BYTES_PER_PAIR = 25.0 / WAVE_D + 9.0   # 20 B read + 5 B written per kernel
 CONFIG2_K = 1 << 20
 CONFIG2_SETS = 4                            # rotating buffer sets: 4 x 83 MB > 126 MB of L2
 CONFIG3_Q = 262144
+CONFIG1_Q = 65536
 L2_FLUSH_BYTES = 256 << 20
 E2E_CHUNK_K = 1 << 20
 E2E_CHUNK_Q = 262144
@@ -526,7 +527,7 @@ def case_config1(ctx):
     kernel-only time, end to end through the host pipeline, and the CPU forward beside it."""
     torch = ctx.torch
     from habitat_b200 import batched, hostio, workloads
-    Q = 65536
+    Q = CONFIG1_Q
     with torch.cuda.stream(ctx.stream):
         w1 = workloads.torch_init_mlp_weights("linear")
         f1, r1 = workloads.make_queries("linear", Q, 1001)
@@ -1220,6 +1221,9 @@ def main():
         if tr.get("wave_bytes_per_kernel") is not None:
             line["roofline"]["traffic"] = tr["wave_bytes_per_kernel"] * (sw.khi - sw.klo)
             line["roofline"]["traffic_source"] = tr["wave_source"]
+        if tr.get("split_bytes_per_query") is not None:
+            mlp["split_precision"]["roofline"]["traffic"] = tr["split_bytes_per_query"] * CONFIG1_Q
+            mlp["split_precision"]["roofline"]["traffic_source"] = tr["split_source"]
         if tr.get("mlp_bytes_per_query") is not None:
             mlp["roofline"]["traffic"] = tr["mlp_bytes_per_query"] * nq
             mlp["roofline"]["traffic_source"] = tr["mlp_source"]
@@ -1311,9 +1315,10 @@ def traffic_from_profiles():
     (a line `dram_bytes_per_kernel: X` / `dram_bytes_per_query: X` in each)."""
     out = {}
     for key, fname, field in (("wave", "wave_scale_lut_kernel__config2.md", "dram_bytes_per_kernel"),
-                              ("mlp", "mlp_chain_pair_kernel__config3.md", "dram_bytes_per_query")):
+                              ("mlp", "mlp_chain_pair_kernel__config3.md", "dram_bytes_per_query"),
+                              ("split", "mlp_chain_pair_kernel__config1_split.md", "dram_bytes_per_query")):
         path = os.path.join(ROOT, "profiles", fname)
-        unit = "wave_bytes_per_kernel" if key == "wave" else "mlp_bytes_per_query"
+        unit = {"wave": "wave_bytes_per_kernel", "mlp": "mlp_bytes_per_query", "split": "split_bytes_per_query"}[key]
         out[unit] = None
         try:
             for ln in open(path):
